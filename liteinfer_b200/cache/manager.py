@@ -42,6 +42,7 @@ class KVGroup:
     allocator: PageAllocator
     page_size: int
     pool: torch.Tensor | None = None     # [len(holders), 2, pages, kv_heads, page_size, head_dim]
+    v_pool: torch.Tensor | None = None   # values of another size than keys: [len(holders), pages, kv_heads, page_size, value dim] (pool then holds keys only, its second axis 1)
     tables: dict[str, list[int]] = field(default_factory=dict)
 
     @property
@@ -50,7 +51,13 @@ class KVGroup:
         return [stop for stop, _ in self.holders]
 
     def bytes_per_page(self, element_size: int) -> int:
-        return len(self.holders) * 2 * self.need.kv_heads * self.page_size * self.need.head_dim * element_size
+        return (len(self.holders) * self.need.kv_heads * self.page_size * (self.need.head_dim + self.need.value_dim)
+                * element_size)
+
+    @property
+    def kept_blocks(self) -> int:
+        """Leading blocks that a window never passes: those of the first tokens that stay visible."""
+        return _cdiv(self.need.keep_first, self.page_size) if self.need.window is not None else 0
 
     def pages_at(self, total: int, largest_step: int) -> int:
         """The most pages a request holds here at any time on its way to `total` tokens, when no step brings it
@@ -60,7 +67,7 @@ class KVGroup:
         if self.need.window is None:
             return every
         span = self.need.window - 1 + max(1, min(largest_step, total))
-        return min(every, _cdiv(span, self.page_size) + 1)
+        return min(every, _cdiv(span, self.page_size) + 1 + self.kept_blocks)
 
     def first_needed_block(self, total: int) -> int:
         """First logical block a request holding `total` tokens can still read."""
@@ -129,9 +136,14 @@ class CacheManager:
                     raise TypeError(f"unknown cache need {need!r}")
         if allocate_storage:
             for group in self.groups:
+                need = group.need
+                same = need.value_dim == need.head_dim
                 group.pool = torch.zeros(
-                    (len(group.holders), 2, num_pages, group.need.kv_heads, page_size, group.need.head_dim),
+                    (len(group.holders), 2 if same else 1, num_pages, need.kv_heads, page_size, need.head_dim),
                     dtype=dtype, device=self.device)
+                if not same:
+                    group.v_pool = torch.zeros((len(group.holders), num_pages, need.kv_heads, page_size, need.value_dim),
+                                               dtype=dtype, device=self.device)
 
     # ----------------------------------------------------------- sizes
     def bytes_per_page(self) -> int:
@@ -242,10 +254,11 @@ class CacheManager:
                 continue
             table = group.tables[request_id]
             passed = min(group.first_needed_block(new_total), len(table))
-            freed = [table[b] for b in range(passed) if table[b] >= 0]
+            kept = group.kept_blocks
+            freed = [table[b] for b in range(kept, passed) if table[b] >= 0]
             if not freed:
                 continue
-            for b in range(passed):
+            for b in range(kept, passed):
                 table[b] = -1
             group.allocator.free(freed)
             self._touch(request_id)
@@ -289,7 +302,8 @@ class CacheManager:
             cache = LayerCache(read_only=entry.cache_of is not None)
             for name, (g, index) in self._stop_kv.get(owner, {}).items():
                 group = self.groups[g]
-                cache.kvs[name] = KVCacheView(group.pool[index, 0], group.pool[index, 1], g, self.page_size)
+                values = group.pool[index, 1] if group.v_pool is None else group.v_pool[index]
+                cache.kvs[name] = KVCacheView(group.pool[index, 0], values, g, self.page_size)
             cache.states.update(self._stop_state.get(owner, {}))
             caches.append(cache)
         return caches

@@ -35,14 +35,18 @@ def register_architecture(name: str, config_class: Any, build_spec: Callable[[An
 
 
 def _builtins() -> None:
+    import liteinfer_b200.architectures.kegizen  # noqa: F401  (registers Kegizen)
     import liteinfer_b200.architectures.llama  # noqa: F401  (registers LlamaForCausalLM)
 
 
 def architecture_name(raw: dict[str, Any], where: str = "config.json") -> str:
+    """The name a config.json chooses its model by: `architectures[0]`, or a plain `architecture` string."""
     architectures = raw.get("architectures") or []
-    if not architectures:
-        raise ConfigError(f"{where} has no 'architectures' field")
-    return str(architectures[0])
+    if architectures:
+        return str(architectures[0])
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    raise ConfigError(f"{where} has neither an 'architectures' nor an 'architecture' field")
 
 
 def resolve(raw: dict[str, Any], where: str = "config.json") -> tuple[Architecture, Any]:

@@ -10,6 +10,10 @@
 // running maximum, sum and the output accumulator are 32-bit; the softmax is
 // the online form (liteinfer/models/paged_kernels.py:216-288).
 //
+// Options: values of another size than keys (`v_dim`; out then has heads * v_dim columns); with a window, the
+// first `keep_first` keys of a sequence stay visible behind it (they are walked first, then the window's keys);
+// `softcap` > 0 turns a scaled score s into softcap * tanh(s / softcap) before the softmax.
+//
 // Work split: block = (query tile, KV head, sequence); its warps take the rows
 // (query, head-in-group) of the tile in turn, one row per warp at a time.  A row
 // walks its keys 32 at a time from the first visible one rounded down to a
@@ -30,8 +34,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __r
                                const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ query_start_loc, const int* __restrict__ context_lens,
-                               int heads, int kv_heads, int head_dim, int page_size, int num_pages, float scale,
-                               int window) {
+                               int heads, int kv_heads, int head_dim, int v_dim, int page_size, int num_pages,
+                               float scale, int window, int keep_first, float softcap) {
   extern __shared__ float q_smem[];  // [warps][head_dim]
   const int seq = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = query_start_loc[seq], q_len = query_start_loc[seq + 1] - q_begin;
@@ -62,51 +66,57 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __r
 #pragma unroll
     for (int i = 0; i < kDimsPerLane; ++i) acc[i] = 0.f;
 
-    for (int base = (first / 32) * 32; base <= qpos; base += 32) {
-      const int kpos = base + lane;
-      const bool valid = kpos >= first && kpos <= qpos;
-      int krow = -1;  // row index of this lane's key inside the pool: (page * kv_heads + kvh) * page_size + slot
-      float s = -INFINITY;
-      if (valid) {
-        const int page = table[kpos / page_size];
-        if (page >= 0 && page < num_pages) {
-          krow = (page * kv_heads + kvh) * page_size + kpos % page_size;
-          const T* kp = k_pool + (size_t)krow * head_dim;
-          float dot = 0.f;
-          for (int d = 0; d < head_dim; ++d) dot += qs[d] * to_float(kp[d]);
-          s = dot * scale;
+    // Two runs of keys: the first tokens that stay visible behind the window, then the window itself.
+    const int kept_end = (window > 0 && keep_first > 0) ? min(keep_first, first) : 0;
+    for (int run = 0; run < 2; ++run) {
+      const int lo = run == 0 ? 0 : first, hi = run == 0 ? kept_end - 1 : qpos;   // inclusive
+      for (int base = (lo / 32) * 32; base <= hi; base += 32) {
+        const int kpos = base + lane;
+        const bool valid = kpos >= lo && kpos <= hi;
+        int krow = -1;  // row index of this lane's key inside the pool: (page * kv_heads + kvh) * page_size + slot
+        float s = -INFINITY;
+        if (valid) {
+          const int page = table[kpos / page_size];
+          if (page >= 0 && page < num_pages) {
+            krow = (page * kv_heads + kvh) * page_size + kpos % page_size;
+            const T* kp = k_pool + (size_t)krow * head_dim;
+            float dot = 0.f;
+            for (int d = 0; d < head_dim; ++d) dot += qs[d] * to_float(kp[d]);
+            s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+          }
         }
-      }
-      const float m_new = fmaxf(m, warp_max(s));
-      if (m_new == -INFINITY) continue;  // nothing visible in this chunk (cannot happen for a valid row)
-      const float p = krow >= 0 ? expf(s - m_new) : 0.f;
-      const float alpha = expf(m - m_new);  // m = -inf on the first chunk gives 0
-      l = l * alpha + warp_sum(p);
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;  // nothing visible in this chunk (cannot happen for a valid row)
+        const float p = krow >= 0 ? expf(s - m_new) : 0.f;
+        const float alpha = expf(m - m_new);  // m = -inf on the first chunk gives 0
+        l = l * alpha + warp_sum(p);
 #pragma unroll
-      for (int i = 0; i < kDimsPerLane; ++i) acc[i] *= alpha;
-      // The probability is rounded to the value type before P.V (paged_kernels.py:282-284).
-      const float p_store = round_to<T>(p);
-      unsigned live = __ballot_sync(0xffffffffu, krow >= 0);
-      while (live) {
-        const int j = __ffs(live) - 1;
-        live &= live - 1;
-        const float pj = __shfl_sync(0xffffffffu, p_store, j);
-        const int vr = __shfl_sync(0xffffffffu, krow, j);
-        const T* vp = v_pool + (size_t)vr * head_dim;
+        for (int i = 0; i < kDimsPerLane; ++i) acc[i] *= alpha;
+        // The probability is rounded to the value type before P.V (paged_kernels.py:282-284).
+        const float p_store = round_to<T>(p);
+        unsigned live = __ballot_sync(0xffffffffu, krow >= 0);
+        while (live) {
+          const int j = __ffs(live) - 1;
+          live &= live - 1;
+          const float pj = __shfl_sync(0xffffffffu, p_store, j);
+          const int vr = __shfl_sync(0xffffffffu, krow, j);
+          const T* vp = v_pool + (size_t)vr * v_dim;
 #pragma unroll
-        for (int i = 0; i < kDimsPerLane; ++i) {
-          const int d = lane + 32 * i;
-          if (d < head_dim) acc[i] += pj * to_float(vp[d]);
+          for (int i = 0; i < kDimsPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < v_dim) acc[i] += pj * to_float(vp[d]);
+          }
         }
+        m = m_new;
       }
-      m = m_new;
     }
-    T* orow = out + (size_t)(q_begin + qi) * out_row_stride + (size_t)head * head_dim;
+    T* orow = out + (size_t)(q_begin + qi) * out_row_stride + (size_t)head * v_dim;
     const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < kDimsPerLane; ++i) {
       const int d = lane + 32 * i;
-      if (d < head_dim) orow[d] = from_float<T>(acc[i] * inv);
+      if (d < v_dim) orow[d] = from_float<T>(acc[i] * inv);
     }
   }
 }
@@ -116,16 +126,17 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __r
 using namespace li;
 
 // q: [tokens, q_row_stride] with head h of a token at columns [h*head_dim, (h+1)*head_dim).
-// out: [tokens, out_row_stride] likewise.  k_pool / v_pool: [num_pages, kv_heads, page_size, head_dim].
-// window <= 0: every earlier key is visible.
+// out: [tokens, out_row_stride] with head h at columns [h*v_dim, (h+1)*v_dim).  k_pool: [num_pages, kv_heads,
+// page_size, head_dim]; v_pool likewise with v_dim.  window <= 0: every earlier key is visible.
 LI_EXPORT int li_paged_attention_generic(int dtype, const void* q, int q_row_stride, void* out, int out_row_stride,
                                          const void* k_pool, const void* v_pool, const int* block_table,
                                          int table_stride, const int* query_start_loc, const int* context_lens,
                                          int num_seqs, int max_q_len, int heads, int kv_heads, int head_dim,
-                                         int page_size, int num_pages, float scale, int window,
-                                         cudaStream_t stream) {
+                                         int v_dim, int page_size, int num_pages, float scale, int window,
+                                         int keep_first, float softcap, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (head_dim < 1 || head_dim > kMaxHeadDim || kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
+  if (v_dim < 1 || v_dim > kMaxHeadDim) return LI_ERR_UNSUPPORTED;
   if (kv_heads > 65535 || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
   const int threads = 256;
   const dim3 grid((max_q_len + kQueriesPerBlock - 1) / kQueriesPerBlock, kv_heads, num_seqs);
@@ -133,12 +144,12 @@ LI_EXPORT int li_paged_attention_generic(int dtype, const void* q, int q_row_str
   if (dtype == kFloat32)
     paged_attention_generic_kernel<float><<<grid, threads, smem, stream>>>(
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_pool, (const float*)v_pool,
-        block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, page_size, num_pages,
-        scale, window);
+        block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, v_dim, page_size,
+        num_pages, scale, window, keep_first, softcap);
   else
     paged_attention_generic_kernel<bf16><<<grid, threads, smem, stream>>>(
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
-        block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, page_size, num_pages,
-        scale, window);
+        block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, v_dim, page_size,
+        num_pages, scale, window, keep_first, softcap);
   LI_LAUNCH_CHECK();
 }

@@ -1,0 +1,197 @@
+// Norms of a model whose residual stream is summed in 32-bit, and the casts around that stream.
+//
+//   li_convert             dst = src between float and bfloat16 (rows may be column slices of wider tensors)
+//   li_layernorm           v = x[row] (+ w_d * norm(value[row]));  x[row] = v (optional);  out = w * norm(v)
+//                          norm(v) = (v - mean) / sqrt(var + eps), var = mean of squared deviations; one block a row
+//   li_projection_rmsnorm  x = w * x / sqrt(mean(x^2) + eps) in place over whole rows of one or two neighbouring
+//                          column slices (q and k of a fused projection, each normalised across all its heads)
+//   li_gated_rmsnorm       out = w * x / sqrt(mean(x^2) + eps) * silu(gate) per head; one warp a (token, head)
+//
+// x of li_layernorm may be float while value, weights and out are bfloat16: the stream stays 32-bit, what the
+// products read is rounded once.  Means, variances, the sum into the stream and every product before the final
+// rounding are 32-bit; the variance is taken in a second pass over the centred row, which the block keeps in
+// shared memory.  The order of every sum depends on the row's width only.
+#include "common.cuh"
+
+namespace li {
+
+template <typename S, typename D>
+__global__ void convert_kernel(const S* __restrict__ src, size_t src_stride, D* __restrict__ dst, size_t dst_stride,
+                               int rows, int width) {
+  grid_dependency_wait();
+  const size_t total = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / width, c = i - r * width;
+    dst[r * dst_stride + c] = from_float<D>(to_float(src[r * src_stride + c]));
+  }
+}
+
+// Mean and 1 / sqrt(var + eps) of the `width` floats in `row` (shared memory); with `centre` false the mean is 0.
+__device__ __forceinline__ void row_statistics(const float* row, int width, float eps, bool centre, float* scratch,
+                                               float& mean, float& inv) {
+  mean = 0.f;
+  if (centre) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) s += row[c];
+    mean = block_sum(s, scratch) / (float)width;
+  }
+  float q = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = row[c] - mean;
+    q += d * d;
+  }
+  const float var = block_sum(q, scratch) / (float)width;
+  inv = 1.0f / sqrtf(var + eps);
+}
+
+// T: dtype of value, the weights and out.  X: dtype of the stream x.
+template <typename T, typename X>
+__global__ void __launch_bounds__(1024)
+layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __restrict__ value_weight,
+                 const T* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width, float eps,
+                 float value_eps, int write_stream, int centre) {
+  extern __shared__ float row[];  // [width]
+  __shared__ float scratch[33];
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const size_t at = (size_t)(rows ? rows[r] : r) * width;
+  float mean, inv;
+  if (value != nullptr) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_float(value[at + c]);
+    __syncthreads();
+    row_statistics(row, width, value_eps, true, scratch, mean, inv);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float normed = (row[c] - mean) * inv * to_float(value_weight[c]);
+      const float v = to_float(x[at + c]) + normed;
+      if (write_stream) x[at + c] = from_float<X>(v);
+      row[c] = round_to<X>(v);
+    }
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_float(x[at + c]);
+  }
+  if (out == nullptr) return;
+  __syncthreads();
+  row_statistics(row, width, eps, centre != 0, scratch, mean, inv);
+  T* o = out + (size_t)r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<T>((row[c] - mean) * inv * to_float(weight[c]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+projection_rmsnorm_kernel(T* __restrict__ x, size_t stride, int width_a, const T* __restrict__ weight_a, int width_b,
+                          const T* __restrict__ weight_b, float eps) {
+  __shared__ float scratch[33];
+  grid_dependency_wait();
+  const bool second = blockIdx.y == 1;
+  T* p = x + (size_t)blockIdx.x * stride + (second ? width_a : 0);
+  const int width = second ? width_b : width_a;
+  const T* w = second ? weight_b : weight_a;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float(p[c]);
+    q += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(q, scratch) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) p[c] = from_float<T>(to_float(p[c]) * inv * to_float(w[c]));
+}
+
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ gate, size_t gate_stride,
+                                     const float* __restrict__ weight, T* __restrict__ out, int tokens, int heads,
+                                     int size, float eps) {
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (token, head)
+  if (item >= (size_t)tokens * heads) return;
+  const size_t t = item / heads;
+  const int h = (int)(item - t * heads);
+  const float* xr = x + (t * heads + h) * size;
+  float q = 0.f;
+  for (int c = lane; c < size; c += 32) q += xr[c] * xr[c];
+  const float inv = 1.0f / sqrtf(warp_sum(q) / (float)size + eps);
+  const T* g = gate + t * gate_stride + (size_t)h * size;
+  T* o = out + (t * heads + h) * size;
+  for (int c = lane; c < size; c += 32) {
+    const float z = to_float(g[c]);
+    o[c] = from_float<T>(xr[c] * inv * weight[c] * (z / (1.0f + expf(-z))));
+  }
+}
+
+template <typename S>
+int convert_from(int dst_dtype, const void* src, size_t ss, void* dst, size_t ds, int rows, int width, dim3 grid,
+                 cudaStream_t stream) {
+  if (dst_dtype == kFloat32)
+    return (int)launch_pdl(rows, convert_kernel<S, float>, grid, dim3(256), 0, stream, (const S*)src, ss, (float*)dst,
+                           ds, rows, width);
+  return (int)launch_pdl(rows, convert_kernel<S, bf16>, grid, dim3(256), 0, stream, (const S*)src, ss, (bf16*)dst, ds,
+                         rows, width);
+}
+
+}  // namespace li
+
+using namespace li;
+
+LI_EXPORT int li_convert(int src_dtype, const void* src, size_t src_stride, int dst_dtype, void* dst, size_t dst_stride,
+                         int rows, int width, cudaStream_t stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  const size_t total = (size_t)rows * width;
+  const dim3 grid((unsigned)((total + 1023) / 1024 < 4096 ? (total + 1023) / 1024 : 4096));
+  if (src_dtype == kFloat32) return convert_from<float>(dst_dtype, src, src_stride, dst, dst_stride, rows, width, grid, stream);
+  return convert_from<bf16>(dst_dtype, src, src_stride, dst, dst_stride, rows, width, grid, stream);
+}
+
+// dtype: of value, value_weight, weight and out.  x_dtype: of the stream x.  flags: 1 = store the sum back into
+// x, 2 = the norm of the sum is not centred (a root-mean-square norm).  value == null: no delta.  out == null:
+// only the sum is made.
+LI_EXPORT int li_layernorm(int dtype, void* x, int x_dtype, const void* value, const void* value_weight,
+                           const void* weight, void* out, const int* rows, int n, int width, float eps,
+                           float value_eps, int flags, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (width < 1 || (size_t)width * sizeof(float) > 200 * 1024) return LI_ERR_UNSUPPORTED;
+  if (dtype == kFloat32 && x_dtype != kFloat32) return LI_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)width * sizeof(float);
+  const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
+  const int write_stream = flags & 1, centre = (flags & 2) ? 0 : 1;
+#define LI_LAUNCH_NORM(T, X)                                                                                          \
+  {                                                                                                                   \
+    if (smem > 48 * 1024) {                                                                                           \
+      cudaError_t e = cudaFuncSetAttribute(layernorm_kernel<T, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    return (int)launch_pdl(n, layernorm_kernel<T, X>, dim3(n), dim3(threads), smem, stream, (X*)x, (const T*)value,   \
+                           (const T*)value_weight, (const T*)weight, (T*)out, rows, width, eps, value_eps,            \
+                           write_stream, centre);                                                                     \
+  }
+  if (dtype == kFloat32) LI_LAUNCH_NORM(float, float)
+  if (x_dtype == kFloat32) LI_LAUNCH_NORM(bf16, float)
+  LI_LAUNCH_NORM(bf16, bf16)
+#undef LI_LAUNCH_NORM
+}
+
+LI_EXPORT int li_projection_rmsnorm(int dtype, void* x, size_t stride, int rows, int width_a, const void* weight_a,
+                                    int width_b, const void* weight_b, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width_a < 1 || width_b < 0) return LI_ERR_UNSUPPORTED;
+  const dim3 grid(rows, width_b > 0 ? 2 : 1);
+  const int widest = width_a > width_b ? width_a : width_b;
+  const int threads = widest >= 4096 ? 1024 : widest >= 1024 ? 512 : 256;
+  if (dtype == kFloat32)
+    return (int)launch_pdl(rows, projection_rmsnorm_kernel<float>, grid, dim3(threads), 0, stream, (float*)x, stride,
+                           width_a, (const float*)weight_a, width_b, (const float*)weight_b, eps);
+  return (int)launch_pdl(rows, projection_rmsnorm_kernel<bf16>, grid, dim3(threads), 0, stream, (bf16*)x, stride, width_a,
+                         (const bf16*)weight_a, width_b, (const bf16*)weight_b, eps);
+}
+
+LI_EXPORT int li_gated_rmsnorm(int dtype, const float* x, const void* gate, size_t gate_stride, const float* weight,
+                               void* out, int tokens, int heads, int size, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads < 1 || size < 1) return LI_ERR_UNSUPPORTED;
+  const size_t items = (size_t)tokens * heads;
+  const int warps = 8;
+  const dim3 grid((unsigned)((items + warps - 1) / warps));
+  if (dtype == kFloat32)
+    return (int)launch_pdl(tokens, gated_rmsnorm_kernel<float>, grid, dim3(warps * 32), 0, stream, x, (const float*)gate,
+                           gate_stride, weight, (float*)out, tokens, heads, size, eps);
+  return (int)launch_pdl(tokens, gated_rmsnorm_kernel<bf16>, grid, dim3(warps * 32), 0, stream, x, (const bf16*)gate,
+                         gate_stride, weight, (bf16*)out, tokens, heads, size, eps);
+}

@@ -10,6 +10,9 @@
 // half-split: dimension j pairs with j + rotary_dim/2 (llama.py:89-102).
 // Dimensions from rotary_dim on pass through unrotated.
 //
+// Values may have another size than keys (`v_dim`): the row is then [q heads | k heads | v heads of v_dim] and the
+// value pool's last axis is v_dim.  `cs_scale` multiplies every cosine and sine (1 for a plain rotation).
+//
 // A page holds `page_size` tokens of every KV head: pool[page][kv_head][slot][dim].
 // The page of a token is block_table[seq][position / page_size]; a negative entry
 // (a page already given back) skips the write.
@@ -22,7 +25,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                      int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ inv_freq, int heads, int kv_heads, int head_dim,
-                                     int rotary_dim, int page_size, int num_pages) {
+                                     int rotary_dim, int page_size, int num_pages, int v_dim, float cs_scale) {
   extern __shared__ float cs[];  // cos[half], sin[half]
   const int t = blockIdx.x;
   grid_launch_dependents();
@@ -32,15 +35,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   float* sinv = cs + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float angle = __fmul_rn((float)pos, inv_freq[i]);
-    cosv[i] = cosf(angle);
-    sinv[i] = sinf(angle);
+    cosv[i] = cs_scale == 1.0f ? cosf(angle) : __fmul_rn(cosf(angle), cs_scale);
+    sinv[i] = cs_scale == 1.0f ? sinf(angle) : __fmul_rn(sinf(angle), cs_scale);
   }
   const int seq = seq_of_token[t];
   const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];   // a row of padding belongs to no sequence
   grid_dependency_wait();           // q, k and v come from the projection before this kernel
   __syncthreads();
 
-  const int row_width = (heads + 2 * kv_heads) * head_dim;
+  const int row_width = (heads + kv_heads) * head_dim + kv_heads * v_dim;
   T* row = qkv + (size_t)t * row_width;
 
   // q: rotate in place.  Work item = (head, pair index or pass-through dim).
@@ -72,7 +75,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
       kv = to_float(krow[w]);
     }
     k_pool[dst] = from_float<T>(kv);
-    v_pool[dst] = vrow[w];
+  }
+  for (int w = threadIdx.x; w < kv_heads * v_dim; w += blockDim.x) {
+    const int h = w / v_dim, j = w - h * v_dim;
+    v_pool[(((size_t)page * kv_heads + h) * page_size + slot) * v_dim + j] = vrow[w];
   }
 }
 
@@ -138,23 +144,25 @@ using namespace li;
 LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const int* seq_of_token,
                                const int* block_table, int table_stride, void* k_pool, void* v_pool,
                                const float* inv_freq, int tokens, int heads, int kv_heads, int head_dim,
-                               int rotary_dim, int page_size, int num_pages, cudaStream_t stream) {
+                               int rotary_dim, int page_size, int num_pages, int v_dim, float cs_scale,
+                               cudaStream_t stream) {
   if (tokens == 0) return 0;
+  if (v_dim < 1) return LI_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
   if (rotary_dim > 0 && inv_freq == nullptr) return LI_ERR_UNSUPPORTED;
   const size_t smem = (size_t)rotary_dim * sizeof(float);
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   const int block = 256;
-  if (dtype == kBFloat16 && rotary_dim == head_dim && head_dim % 16 == 0 && aligned16(qkv) && aligned16(k_pool) &&
-      aligned16(v_pool))
+  if (dtype == kBFloat16 && rotary_dim == head_dim && head_dim % 16 == 0 && v_dim == head_dim && cs_scale == 1.0f &&
+      aligned16(qkv) && aligned16(k_pool) && aligned16(v_pool))
     return (int)launch_pdl(tokens, rope_kv_write_vec_kernel, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv,
                            positions, seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq,
                            heads, kv_heads, head_dim, page_size, num_pages);
   if (dtype == kFloat32)
     return (int)launch_pdl(tokens, rope_kv_write_kernel<float>, dim3(tokens), dim3(block), smem, stream, (float*)qkv,
                            positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool,
-                           inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages);
+                           inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim, cs_scale);
   return (int)launch_pdl(tokens, rope_kv_write_kernel<bf16>, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv, positions,
                          seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
-                         kv_heads, head_dim, rotary_dim, page_size, num_pages);
+                         kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim, cs_scale);
 }

@@ -41,10 +41,25 @@ _SIGNATURES = {
     "li_act_mul": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_act_mul_interleaved": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                        c_void_p]),
     "li_paged_attention_generic": ("attention_generic", [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p]),
+    "li_convert": ("layernorm", [c_int, c_void_p, c_size_t, c_int, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "li_layernorm": ("layernorm", [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "li_projection_rmsnorm": ("layernorm", [c_int, c_void_p, c_size_t, c_int, c_int, c_void_p, c_int, c_void_p,
+                                            c_float, c_void_p]),
+    "li_gated_rmsnorm": ("layernorm", [c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int,
+                                       c_float, c_void_p]),
+    "li_short_conv": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "li_short_conv_update": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_void_p]),
+    "li_gated_delta_rule": ("delta_rule", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_void_p]),
     "li_paged_attention_mma": ("attention_mma", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -595,25 +610,29 @@ def act_mul_interleaved(gate_up: torch.Tensor, out: torch.Tensor, activation: st
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                   block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                   inv_freq: torch.Tensor | None, heads: int, kv_heads: int, head_dim: int,
-                  rotary_dim: int, store: bool = True) -> None:
+                  rotary_dim: int, store: bool = True, v_head_dim: int | None = None,
+                  cos_sin_scale: float = 1.0) -> None:
     """Rotates q (in place) and k, and stores k and v of every token into its page
     (with `store` False only q is rotated; the pages are left alone).
 
-    qkv: [tokens, (heads + 2*kv_heads) * head_dim].  k_pool, v_pool:
-    [pages, kv_heads, page_size, head_dim].  block_table: [seqs, max_pages] int32.
+    qkv: [tokens, (heads + kv_heads) * head_dim + kv_heads * v_head_dim].  k_pool:
+    [pages, kv_heads, page_size, head_dim], v_pool likewise with `v_head_dim` (None: head_dim).
+    block_table: [seqs, max_pages] int32.  `cos_sin_scale` multiplies every cosine and sine.
     """
     _on_gpu(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq)
     _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
     tokens = qkv.shape[0]
     pages, kvh, page_size, hd = k_pool.shape
-    assert (kvh, hd) == (kv_heads, head_dim) and v_pool.shape == k_pool.shape
-    assert qkv.shape[1] == (heads + 2 * kv_heads) * head_dim
+    vd = head_dim if v_head_dim is None else v_head_dim
+    assert (kvh, hd) == (kv_heads, head_dim) and v_pool.shape == (pages, kv_heads, page_size, vd)
+    assert qkv.shape[1] == (heads + kv_heads) * head_dim + kv_heads * vd
     assert k_pool.dtype == qkv.dtype == v_pool.dtype
     assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rotary_dim)
     _check(_fn("li_rope_kv_write")(_code(qkv), qkv.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
                                    block_table.data_ptr(), block_table.stride(0), k_pool.data_ptr(),
                                    v_pool.data_ptr(), _ptr(inv_freq), tokens, heads, kv_heads, head_dim,
-                                   rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0, _stream()),
+                                   rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0,
+                                   vd, float(cos_sin_scale), _stream()),
            "rope_kv_write")
 
 
@@ -673,14 +692,17 @@ def cluster_capacity(head_dim: int, splits: int) -> int:
 
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
-                            num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0) -> torch.Tensor:
-    """The plain SIMT kernel: any dtype, head size up to 256, any grouping."""
+                            num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, keep_first=0,
+                            softcap=0.0) -> torch.Tensor:
+    """The plain SIMT kernel: any dtype, key and value sizes up to 256 (they may differ), any grouping, a window
+    that may keep the first `keep_first` keys visible, scores capped by softcap * tanh(score / softcap)."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     pages, kvh, page_size, hd = k_pool.shape
     _check(_fn("li_paged_attention_generic")(
         _code(q), q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
-        num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window), _stream()),
+        num_seqs, max_q_len, heads, kv_heads, head_dim, v_pool.shape[3], page_size, pages, float(scale), int(window),
+        int(keep_first), float(softcap), _stream()),
         "paged_attention_generic")
     return out
 
@@ -776,7 +798,8 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                     v_pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
                     context_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int, kv_heads: int,
                     head_dim: int, scale: float, window: int = 0, plan=None,
-                    decode_splits: int | None = None, newest: "NewestToken | None" = None) -> torch.Tensor:
+                    decode_splits: int | None = None, newest: "NewestToken | None" = None, keep_first: int = 0,
+                    softcap: float = 0.0) -> torch.Tensor:
     """Attention of each sequence's newest queries over its pages (any mix of portions and single tokens).
 
     q: the tensor holding the queries, head h of token t at q[t, h*head_dim:...]
@@ -786,6 +809,9 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     token go through a launch that splits their keys over several blocks, the
     others through an unsplit one.  Everything else runs the plain SIMT kernel.
     `newest`: only where `fused_decode_supports` said yes; see `paged_attention_mma`.
+    `keep_first` (with a window): the first keys of a sequence stay visible behind the window.  `softcap` > 0:
+    a scaled score s becomes softcap * tanh(s / softcap).  Values may have another size than keys
+    (`v_pool.shape[3]`); out is then [tokens, heads * value size].
     """
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
@@ -793,9 +819,12 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     assert (kvh, hd) == (kv_heads, head_dim) and q.dtype == out.dtype == k_pool.dtype == v_pool.dtype
     if newest is not None and not fused_decode_supports(q.dtype, heads, kv_heads, head_dim, head_dim, plan):
         raise ValueError("the decode kernel with the rotary encoding fused in does not take this step")
-    if not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
+    plain = softcap <= 0 and (keep_first <= 0 or window <= 0) and v_pool.shape[3] == head_dim
+    if not plain or not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
+        assert newest is None
         return paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc,
-                                       context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
+                                       context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
+                                       keep_first, softcap)
     common = (q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     if plan is None:
         return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
@@ -810,6 +839,176 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
         splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound, head_dim, streaming)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
                             window, splits, newest, streaming)
+    return out
+
+
+# ------------------------------------------------- 32-bit stream, layer norm, recurrences
+@dataclass
+class NormedDelta:
+    """A delta of the residual stream that has not been computed yet: weight * layer_norm(value), the output of a
+    sublayer that is normalised before it is added.  The norm that reads the stream next adds it on its way."""
+
+    value: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+
+def _rows2d(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelLibraryError(f"{what} must be two-dimensional with contiguous rows (a column slice is fine)")
+    if not t.is_cuda:
+        raise KernelLibraryError(f"liteinfer_b200 kernels run on a CUDA device only; there is no CPU path (got {t.device})")
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """dst[r, c] = src[r, c], between float32 and bfloat16 in either direction (or a copy); both may be column
+    slices of wider tensors."""
+    _rows2d(src, "src"); _rows2d(dst, "dst")
+    assert src.shape == dst.shape
+    rows, width = src.shape
+    _check(_fn("li_convert")(_code(src), src.data_ptr(), src.stride(0), _code(dst), dst.data_ptr(), dst.stride(0),
+                             rows, width, _stream()), "convert")
+    return dst
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              delta: "NormedDelta | None" = None, rows: torch.Tensor | None = None,
+              write_stream: bool = False, centre: bool = True) -> torch.Tensor:
+    """out[r] = weight * norm(v), v = x[row] (+ delta.weight * norm(delta.value[row])), row = rows[r] if given else r;
+    norm(v) = (v - mean) / sqrt(var + eps) (with `centre` False: v / sqrt(mean(v^2) + eps)).  With `write_stream`
+    v is stored back into x.  x may be float32 whatever the dtype of out and the weights (a 32-bit residual
+    stream); every statistic and the sum are 32-bit."""
+    _on_gpu(x, weight, out, rows, delta.value if delta else None, delta.weight if delta else None)
+    _int32(rows, "rows")
+    width = x.shape[-1]
+    n = out.shape[0]
+    assert weight.numel() == width and out.shape[-1] == width and out.dtype == weight.dtype
+    assert x.dtype in (torch.float32, out.dtype)
+    assert rows is None or rows.numel() == n
+    assert rows is not None or n == x.shape[0]
+    assert delta is None or (delta.value.shape == x.shape and delta.value.dtype == out.dtype
+                             and delta.weight.dtype == out.dtype)
+    assert not (write_stream and (delta is None or rows is not None))
+    _check(_fn("li_layernorm")(_code(out), x.data_ptr(), _code(x), _ptr(delta.value if delta else None),
+                               _ptr(delta.weight if delta else None), weight.data_ptr(), out.data_ptr(), _ptr(rows),
+                               n, width, float(eps), float(delta.eps if delta else 0.0),
+                               int(write_stream) | (0 if centre else 2), _stream()), "layernorm")
+    return out
+
+
+def layernorm_add(stream: torch.Tensor, value: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """stream += weight * layer_norm(value): `stream` float32 or the dtype of value; summed in 32-bit."""
+    _on_gpu(stream, value, weight)
+    assert stream.shape == value.shape and value.dtype == weight.dtype and stream.dtype in (torch.float32, value.dtype)
+    _check(_fn("li_layernorm")(_code(value), stream.data_ptr(), _code(stream), value.data_ptr(), weight.data_ptr(),
+                               None, None, None, stream.shape[0], stream.shape[1], 0.0, float(eps), 1, _stream()),
+           "layernorm_add")
+    return stream
+
+
+def projection_rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x[r] = weight * x[r] / sqrt(mean(x[r]^2) + eps) in place over whole rows of `x`, which may be a column
+    slice of a wider tensor (the q or k part of a fused projection, normalised across all its heads at once)."""
+    _rows2d(x, "x")
+    _on_gpu(weight)
+    rows, width = x.shape
+    assert weight.numel() == width and weight.dtype == x.dtype
+    _check(_fn("li_projection_rmsnorm")(_code(x), x.data_ptr(), x.stride(0), rows, width, weight.data_ptr(), 0, None,
+                                        float(eps), _stream()), "projection_rmsnorm")
+    return x
+
+
+def qk_projection_rmsnorm_(q: torch.Tensor, q_weight: torch.Tensor, k: torch.Tensor, k_weight: torch.Tensor,
+                           eps: float) -> None:
+    """`projection_rmsnorm_` of two neighbouring column slices of one tensor (q, then k) in one launch."""
+    _rows2d(q, "q"); _rows2d(k, "k")
+    _on_gpu(q_weight, k_weight)
+    assert q.stride(0) == k.stride(0) and q.shape[0] == k.shape[0] and q.dtype == k.dtype == q_weight.dtype
+    assert k.data_ptr() == q.data_ptr() + q.shape[1] * q.element_size()
+    assert q_weight.numel() == q.shape[1] and k_weight.numel() == k.shape[1]
+    _check(_fn("li_projection_rmsnorm")(_code(q), q.data_ptr(), q.stride(0), q.shape[0], q.shape[1],
+                                        q_weight.data_ptr(), k.shape[1], k_weight.data_ptr(), float(eps), _stream()),
+           "projection_rmsnorm")
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  heads: int) -> torch.Tensor:
+    """out[t, h] = weight * x[t, h] / sqrt(mean(x[t, h]^2) + eps) * silu(gate[t, h]) per head of `weight.numel()`
+    entries.  x and weight: float32, x [tokens, heads * size]; gate (a column slice is fine) and out in the engine's dtype."""
+    _on_gpu(x, weight, out)
+    _rows2d(gate, "gate")
+    tokens, width = out.shape
+    size = weight.numel()
+    assert x.dtype == torch.float32 and x.shape == out.shape == gate.shape and width == heads * size
+    assert gate.dtype == out.dtype and weight.dtype == torch.float32
+    _check(_fn("li_gated_rmsnorm")(_code(out), x.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+                                   out.data_ptr(), tokens, heads, size, float(eps), _stream()), "gated_rmsnorm")
+    return out
+
+
+def short_conv(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_token: torch.Tensor,
+               query_start_loc: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
+               activation: str = "silu") -> torch.Tensor:
+    """A short causal convolution over time per channel, then the activation.
+
+    x [tokens, channels] (a column slice is fine): this step's inputs, every sequence's end to end.  taps
+    [channels, K]: column K-1 multiplies the current token, K-2 the one before.  tail [slots, K-1, channels]: the
+    last K-1 inputs of each request before this step (zeros at its start), oldest first; it is read, not written
+    (`short_conv_update` moves it on).  Tokens whose sequence is -1 give zeros."""
+    _rows2d(x, "x")
+    _on_gpu(taps, tail, seq_of_token, query_start_loc, state_slots, out)
+    _int32(seq_of_token, "seq_of_token"); _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
+    tokens, channels = x.shape
+    K = taps.shape[1]
+    assert taps.shape[0] == channels and out.shape == (tokens, channels) and out.dtype == x.dtype == taps.dtype
+    assert tail.shape[1:] == (K - 1, channels) and tail.dtype == x.dtype
+    if activation not in ("silu", "none"):
+        raise KernelLibraryError(f"short_conv knows the activations 'silu' and 'none', not {activation!r}")
+    _check(_fn("li_short_conv")(_code(x), x.data_ptr(), x.stride(0), taps.data_ptr(), tail.data_ptr() if K > 1 else None,
+                                seq_of_token.data_ptr(), query_start_loc.data_ptr(), state_slots.data_ptr(),
+                                out.data_ptr(), tokens, channels, K, 1 if activation == "silu" else 0, _stream()),
+           "short_conv")
+    return out
+
+
+def short_conv_update(x: torch.Tensor, tail: torch.Tensor, query_start_loc: torch.Tensor, state_slots: torch.Tensor,
+                      num_seqs: int) -> None:
+    """Moves every sequence's convolution tail on by this step's inputs: afterwards tail[slot] holds the last K-1
+    inputs including this step's (a step shorter than K-1 keeps the newest of the old ones)."""
+    _rows2d(x, "x")
+    _on_gpu(tail, query_start_loc, state_slots)
+    channels = x.shape[1]
+    if tail.shape[1] == 0:
+        return
+    assert tail.shape[2] == channels and tail.dtype == x.dtype
+    _check(_fn("li_short_conv_update")(_code(x), x.data_ptr(), x.stride(0), tail.data_ptr(), query_start_loc.data_ptr(),
+                                       state_slots.data_ptr(), num_seqs, channels, tail.shape[1] + 1, _stream()),
+           "short_conv_update")
+
+
+def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                     state: torch.Tensor, query_start_loc: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
+                     heads: int, kv_heads: int, dim: int, vdim: int, out: torch.Tensor) -> torch.Tensor:
+    """The gated delta rule, token by token, on a 32-bit state per request and head.
+
+    qkv [tokens, 2 * kv_heads * dim + heads * vdim]: q and k (kv_heads heads of dim; head h of the values reads
+    q/k head h // (heads / kv_heads)) and v (heads of vdim), after their convolutions.  ab (a column slice is
+    fine) [tokens, 2 * heads]: per head the raw write strength (beta = sigmoid) and, behind those, the raw decay
+    input (g = exp(-exp(a_log) * softplus(raw + dt_bias))).  q and k are made unit vectors (x / sqrt(sum x^2 +
+    1e-6)), q also times dim^-0.5.  Per token: S *= g; u = beta * (v - S^T k); S += k u^T; o = S^T q.
+    state [slots, heads, dim, vdim] float32 is read and written; out [tokens, heads * vdim] float32."""
+    _on_gpu(qkv, a_log, dt_bias, state, query_start_loc, state_slots, out)
+    _rows2d(ab, "ab")
+    _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
+    tokens = qkv.shape[0]
+    assert qkv.shape[1] == 2 * kv_heads * dim + heads * vdim and ab.shape == (tokens, 2 * heads) and ab.dtype == qkv.dtype
+    assert a_log.dtype == dt_bias.dtype == state.dtype == out.dtype == torch.float32
+    assert a_log.numel() == dt_bias.numel() == heads and state.shape[1:] == (heads, dim, vdim)
+    assert out.shape == (tokens, heads * vdim) and heads % kv_heads == 0
+    _check(_fn("li_gated_delta_rule")(_code(qkv), qkv.data_ptr(), ab.data_ptr(), ab.stride(0), tokens, num_seqs,
+                                      a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), query_start_loc.data_ptr(),
+                                      state_slots.data_ptr(), out.data_ptr(), heads, kv_heads, dim, vdim, 0, 0,
+                                      _stream()), "gated_delta_rule")
     return out
 
 

@@ -28,16 +28,30 @@ class Attention:
     on q and k, keys and values stored, attention of the new queries over
     everything stored, output projection.  Query head h reads KV head
     h // (heads // kv_heads); scores are scaled by `scale` (head_dim^-0.5 unless
-    given).  `window` keeps only the newest `window` keys visible.  The three
+    given).  `window` keeps only the newest `window` keys visible, and beside
+    them the first `keep_first` of the sequence.  `v_head_dim`: values of another
+    size than keys.  `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap).
+    `qk_norm` "projection": q and k are each divided by their root mean square over the
+    whole projection (all heads at once; eps `qk_norm_eps`) and multiplied by the weights
+    `q_norm.weight` / `k_norm.weight`, before the position encoding.  The three
     projections are one product against the concatenated weights.
     """
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, bias: bool = False, out_bias: bool | None = None,
-                 window: int | None = None, scale: float | None = None, cache_name: str = "kv") -> None:
+                 window: int | None = None, scale: float | None = None, cache_name: str = "kv",
+                 v_head_dim: int | None = None, keep_first: int = 0, softcap: float = 0.0,
+                 qk_norm: str | None = None, qk_norm_eps: float = 1e-6) -> None:
         if heads % kv_heads:
             raise ValueError(f"heads={heads} is not a multiple of kv_heads={kv_heads}")
+        if qk_norm not in (None, "projection"):
+            raise ValueError(f"qk_norm {qk_norm!r} is not supported; known: None, 'projection'")
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
+        self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
+        self.keep_first = int(keep_first) if window is not None else 0
+        self.softcap = float(softcap or 0.0)
+        self.qk_norm, self.qk_norm_eps = qk_norm, float(qk_norm_eps)
+        self.q_norm_weight = self.k_norm_weight = None
         self.bias = bias
         self.out_bias = bias if out_bias is None else out_bias
         self.window = window
@@ -51,16 +65,19 @@ class Attention:
         self.o_bias: torch.Tensor | None = None
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        q, kv = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        q, kv, v = self.heads * self.head_dim, self.kv_heads * self.head_dim, self.kv_heads * self.v_head_dim
         specs = {
             "q_proj.weight": TensorSpec((q, self.hidden_size)),
             "k_proj.weight": TensorSpec((kv, self.hidden_size)),
-            "v_proj.weight": TensorSpec((kv, self.hidden_size)),
-            "o_proj.weight": TensorSpec((self.hidden_size, q)),
+            "v_proj.weight": TensorSpec((v, self.hidden_size)),
+            "o_proj.weight": TensorSpec((self.hidden_size, self.heads * self.v_head_dim)),
         }
+        if self.qk_norm:
+            specs.update({"q_norm.weight": TensorSpec((q,), init="ones_normal"),
+                          "k_norm.weight": TensorSpec((kv,), init="ones_normal")})
         if self.bias:
             specs.update({"q_proj.bias": TensorSpec((q,), init="zeros"), "k_proj.bias": TensorSpec((kv,), init="zeros"),
-                          "v_proj.bias": TensorSpec((kv,), init="zeros")})
+                          "v_proj.bias": TensorSpec((v,), init="zeros")})
         if self.out_bias:
             specs["o_proj.bias"] = TensorSpec((self.hidden_size,), init="zeros")
         for name, spec in self.position.tensor_specs().items():
@@ -72,11 +89,15 @@ class Attention:
         if self.bias:
             self.qkv_bias = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]])
         self.o_weight = tensors["o_proj.weight"]
+        if self.qk_norm:
+            self.q_norm_weight, self.k_norm_weight = tensors["q_norm.weight"], tensors["k_norm.weight"]
         self.o_bias = tensors.get("o_proj.bias") if self.out_bias else None
         self.position.bind({n[len("position."):]: t for n, t in tensors.items() if n.startswith("position.")})
 
     def cache_needs(self) -> tuple:
-        return (KVNeed(self.kv_heads, self.head_dim, self.window, name=self.cache_name),)
+        return (KVNeed(self.kv_heads, self.head_dim, self.window, name=self.cache_name,
+                       v_head_dim=None if self.v_head_dim == self.head_dim else self.v_head_dim,
+                       keep_first=self.keep_first),)
 
     takes_pending_norm = True       # x may be an ops.PendingNorm: the qkv product folds the norm in
     adds_to_residual = True         # the output projection adds into the residual stream where its kernel can
@@ -84,16 +105,21 @@ class Attention:
     def forward(self, x, ctx: StepContext, cache: LayerCache, residual: torch.Tensor | None = None):
         kv = cache.kvs[self.cache_name]
         tokens = x.shape[0]
-        q_width = self.heads * self.head_dim
-        qkv = torch.empty((tokens, q_width + 2 * self.kv_heads * self.head_dim), dtype=x.dtype, device=x.device)
+        q_width, kv_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        v_width = self.kv_heads * self.v_head_dim
+        qkv = torch.empty((tokens, q_width + kv_width + v_width), dtype=x.dtype, device=x.device)
         ops.linear(x, self.qkv_weight, qkv, self.qkv_bias)
+        if self.qk_norm:
+            ops.qk_projection_rmsnorm_(qkv[:, :q_width], self.q_norm_weight, qkv[:, q_width:q_width + kv_width],
+                                       self.k_norm_weight, self.qk_norm_eps)
         table = ctx.block_tables[kv.group]
         rotary = self.position.rotary()
-        attended = torch.empty((tokens, q_width), dtype=x.dtype, device=x.device)
-        if rotary is not None and ops.fused_decode_supports(x.dtype, self.heads, self.kv_heads, self.head_dim,
-                                                            rotary.rotary_dim, ctx.plan):
+        attended = torch.empty((tokens, self.heads * self.v_head_dim), dtype=x.dtype, device=x.device)
+        masked = dict(keep_first=self.keep_first, softcap=self.softcap) if (self.keep_first or self.softcap) else {}
+        plain = not masked and self.v_head_dim == self.head_dim and (rotary is None or rotary.attention_scaling == 1.0)
+        if plain and rotary is not None and ops.fused_decode_supports(x.dtype, self.heads, self.kv_heads, self.head_dim,
+                                                                      rotary.rotary_dim, ctx.plan):
             # Every sequence brings one token: one launch rotates q and k, stores k and v and attends.
-            kv_width = self.kv_heads * self.head_dim
             newest = ops.NewestToken(rotary.inv_freq, qkv[:, q_width:], qkv[:, q_width + kv_width:],
                                      store=not cache.read_only)
             ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
@@ -102,16 +128,17 @@ class Attention:
                                 decode_splits=ctx.decode_splits, newest=newest)
             return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
         if rotary is None:
-            kv_width = self.kv_heads * self.head_dim
             self.position.apply(qkv[:, :q_width].unflatten(1, (self.heads, self.head_dim)),
                                 qkv[:, q_width:q_width + kv_width].unflatten(1, (self.kv_heads, self.head_dim)), ctx)
+        wide = {} if plain else dict(v_head_dim=self.v_head_dim,
+                                     cos_sin_scale=rotary.attention_scaling if rotary else 1.0)
         ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, kv.k_pool, kv.v_pool,
                           rotary.inv_freq if rotary else None, self.heads, self.kv_heads, self.head_dim,
-                          rotary.rotary_dim if rotary else 0, store=not cache.read_only)
+                          rotary.rotary_dim if rotary else 0, store=not cache.read_only, **wide)
         ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
                             ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
                             self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
-                            decode_splits=ctx.decode_splits)
+                            decode_splits=ctx.decode_splits, **masked)
         return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
 
 

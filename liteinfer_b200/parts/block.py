@@ -33,6 +33,8 @@ def apply_norm(norm, hidden: torch.Tensor, delta, consumer=None, rows: torch.Ten
     """Runs `norm` on the residual stream, whatever form the pending `delta` has (None, a tensor still to be
     added, or `ops.RowStats` of a sum already made), using what the norm and the part that reads its result say
     they can do: a norm that `defers` hands a consumer that `takes_pending_norm` the unfinished norm."""
+    if isinstance(delta, ops.NormedDelta):
+        return norm.forward(hidden, delta) if rows is None else norm.forward(hidden, delta, rows=rows)
     if isinstance(delta, ops.RowStats) and not getattr(norm, "reads_row_stats", False):
         delta = None                # the sum is in `hidden` already; a plain norm needs no more
     lazy = (isinstance(delta, ops.RowStats) and getattr(norm, "defers", False)
@@ -70,4 +72,36 @@ class PreNormResidualBlock:
         return hidden, run_part(self.feed_forward, normed, hidden, ctx)
 
 
+class SandwichNormBlock:
+    """h = h + post(mixer(pre(h))); h = h + post'(feed_forward(pre'(h))): every sublayer is normalised on its way
+    in and on its way out.  The sublayer's normalised output travels as an `ops.NormedDelta`, so the norm that
+    reads the stream next (of this block, the next block, the re-entry part or the model's final norm) does the
+    outgoing norm, the sum and its own norm in one kernel."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "feed_forward_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+
+    def __init__(self, parts: dict) -> None:
+        self.mixer_norm, self.mixer, self.mixer_post_norm = parts["mixer_norm"], parts["mixer"], parts["mixer_post_norm"]
+        self.feed_forward_norm = parts.get("feed_forward_norm")
+        self.feed_forward = parts.get("feed_forward")
+        self.feed_forward_post_norm = parts.get("feed_forward_post_norm")
+
+    def forward(self, hidden: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        normed = apply_norm(self.mixer_norm, hidden, delta)
+        delta = self.mixer_post_norm.normed_delta(self.mixer.forward(normed, ctx, cache))
+        if self.feed_forward is None:
+            return hidden, delta
+        normed = apply_norm(self.feed_forward_norm, hidden, delta)
+        return hidden, self.feed_forward_post_norm.normed_delta(self.feed_forward.forward(normed, ctx))
+
+
+class SandwichNormMixerBlock(SandwichNormBlock):
+    """`SandwichNormBlock` of a layer that has no feed-forward."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm"}
+
+
 register_block("prenorm_residual", PreNormResidualBlock)
+register_block("sandwich_norm", SandwichNormBlock)
+register_block("sandwich_norm_mixer_only", SandwichNormMixerBlock)

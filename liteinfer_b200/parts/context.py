@@ -17,7 +17,9 @@ import torch
 @dataclass(frozen=True)
 class KVNeed:
     """A part that keeps keys and values per token: `window` None keeps every
-    token, a number keeps the newest `window` of them.  `name` is the key under
+    token, a number keeps the newest `window` of them, and beside those the first
+    `keep_first` tokens of the sequence.  `v_head_dim`: the size of a value where
+    it differs from a key's (None: the same).  `name` is the key under
     which the part finds its pages in its layer's `LayerCache.kvs`; a layer whose
     parts declare several needs gives each its own name.  Needs that are equal
     apart from the name share a group of pages."""
@@ -26,6 +28,12 @@ class KVNeed:
     head_dim: int
     window: int | None = None
     name: str = field(default="kv", compare=False)
+    v_head_dim: int | None = None
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -41,7 +49,7 @@ class StateNeed:
 @dataclass
 class KVCacheView:
     k_pool: torch.Tensor       # [pages, kv_heads, page_size, head_dim] of this layer
-    v_pool: torch.Tensor
+    v_pool: torch.Tensor       # [pages, kv_heads, page_size, value dim]
     group: int                 # index into StepContext.block_tables
     page_size: int
 
@@ -102,6 +110,7 @@ class StepContext:
     decode_splits: int | None = None       # EngineConfig.paged_decode_splits
     plan: AttentionPlan | None = None
     extras: dict = field(default_factory=dict)
+    layer_trace: list | None = None        # a list here collects the residual stream after every stop (debugging)
 
     @property
     def is_decode_only(self) -> bool:

@@ -13,14 +13,27 @@ import torch
 
 import liteinfer_b200.parts.attention  # noqa: F401  (registers the built-in parts)
 import liteinfer_b200.parts.block  # noqa: F401
+import liteinfer_b200.parts.delta_rule  # noqa: F401
 import liteinfer_b200.parts.embedding  # noqa: F401
 import liteinfer_b200.parts.feed_forward  # noqa: F401
 import liteinfer_b200.parts.norm  # noqa: F401
 import liteinfer_b200.parts.position  # noqa: F401
+import liteinfer_b200.parts.reentry  # noqa: F401
+from liteinfer_b200 import ops
 from liteinfer_b200.parts.block import apply_norm
 from liteinfer_b200.parts.context import LayerCache, StepContext
 from liteinfer_b200.parts.registry import BLOCKS, build_part
 from liteinfer_b200.parts.spec import ModelSpec, TensorSpec
+
+def _settled(hidden: torch.Tensor, delta) -> torch.Tensor:
+    """A copy of the residual stream with the pending delta added (for `StepContext.layer_trace`)."""
+    out = hidden.clone()
+    if isinstance(delta, ops.NormedDelta):
+        ops.layernorm_add(out, delta.value, delta.weight, delta.eps)
+    elif isinstance(delta, torch.Tensor):
+        ops.add_(out, delta)
+    return out
+
 
 class Layer:
     """One layer: its block class says which roles it has and from which registry each is built
@@ -52,23 +65,30 @@ class Model:
         self.layers = [Layer(layer, dtype, device) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, dtype=dtype, device=device)
         self.head = build_part("head", spec.head, dtype=dtype, device=device)
+        self.reentry = (build_part("reentry", spec.reentry, dtype=dtype, device=device)
+                        if spec.reentry is not None else None)
         self.schedule = spec.schedule
+        self.wide_stream = spec.stream_dtype == "float32" and dtype != torch.float32
 
     # ------------------------------------------------------------- tensors
     def _named_parts(self):
-        yield self.spec.embedding_prefix, self.embedding
+        """(prefix, part, {the part's own tensor name: its name behind the prefix}) of every part."""
+        renames = self.spec.renames
+        yield self.spec.embedding_prefix, self.embedding, renames.get("embedding", {})
         for layer in self.layers:
             for role, part in layer.parts.items():
-                yield layer.spec.prefixes[role], part
-        yield self.spec.final_norm_prefix, self.final_norm
-        yield self.spec.head_prefix, self.head
+                yield layer.spec.prefixes[role], part, layer.spec.renames.get(role, {})
+        if self.reentry is not None:
+            yield self.spec.reentry_prefix, self.reentry, renames.get("reentry", {})
+        yield self.spec.final_norm_prefix, self.final_norm, renames.get("final_norm", {})
+        yield self.spec.head_prefix, self.head, renames.get("head", {})
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Checkpoint name -> spec of every tensor the parts read, in a fixed order."""
         specs: dict[str, TensorSpec] = {}
-        for prefix, part in self._named_parts():
+        for prefix, part, renames in self._named_parts():
             for local, spec in part.tensor_specs().items():
-                name = prefix + local
+                name = prefix + renames.get(local, local)
                 if name in specs and specs[name] != spec:
                     raise ValueError(f"two parts want tensor {name!r} with different specs")
                 specs[name] = spec
@@ -76,18 +96,18 @@ class Model:
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         """Hand every part its tensors (by checkpoint name, already on the device)."""
-        for prefix, part in self._named_parts():
-            part.bind({local: tensors[prefix + local] for local in part.tensor_specs()})
+        for prefix, part, renames in self._named_parts():
+            part.bind({local: tensors[prefix + renames.get(local, local)] for local in part.tensor_specs()})
 
     @property
     def graph_safe(self) -> bool:
         """Whether a step of this model may be captured into a CUDA graph: every part launches kernels only.
         A part that reads device values on the host in `forward` sets `graph_safe = False`."""
-        return all(getattr(part, "graph_safe", True) for _, part in self._named_parts())
+        return all(getattr(part, "graph_safe", True) for _, part, _ in self._named_parts())
 
     def weight_bytes(self) -> int:
         seen: dict[int, int] = {}
-        for _, part in self._named_parts():
+        for _, part, _ in self._named_parts():
             for value in vars(part).values():
                 if isinstance(value, torch.Tensor):
                     seen[value.data_ptr()] = value.numel() * value.element_size()
@@ -101,10 +121,19 @@ class Model:
     # ------------------------------------------------------------- forward
     def hidden(self, ctx: StepContext, caches: list[LayerCache]) -> tuple[torch.Tensor, torch.Tensor | None]:
         """Runs the schedule; returns the residual stream and the delta still to be added."""
-        hidden = self.embedding.forward(ctx.token_ids)
+        embedded = hidden = self.embedding.forward(ctx.token_ids)
+        if self.wide_stream:
+            # The stream is summed in 32-bit: the embedding's rows are widened once, every layer adds in place.
+            hidden = ops.convert(embedded, torch.empty(embedded.shape, dtype=torch.float32, device=embedded.device))
+        elif self.reentry is not None:
+            hidden = embedded.clone()       # the layers add into the stream in place; the embedding's output is read again
         delta = None
         for stop, entry in enumerate(self.schedule):
+            if entry.reenter:
+                hidden, delta = self.reentry.forward(hidden, delta, embedded)
             hidden, delta = self.layers[entry.layer].block.forward(hidden, delta, ctx, caches[stop])
+            if ctx.layer_trace is not None:
+                ctx.layer_trace.append(_settled(hidden, delta))
         return hidden, delta
 
     def forward(self, ctx: StepContext, caches: list[LayerCache]) -> torch.Tensor:

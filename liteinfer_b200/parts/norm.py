@@ -58,4 +58,38 @@ class RMSNorm:
                            write_residual=delta is not None and rows is None)
 
 
+class LayerNorm:
+    """y = weight * (x - mean) / sqrt(var + eps), var the mean of the squared deviations; no bias.
+
+    The stream `x` may be 32-bit whatever the engine's dtype: the norm reads it as it is and writes its result
+    in the engine's dtype.  `delta` may be an `ops.NormedDelta` (the sublayer before is itself normalised before
+    it is added): one kernel normalises the delta, adds it into the stream and normalises the sum."""
+
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+        self.size, self.eps, self.dtype, self.device = size, float(eps), dtype, device
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.size,), init="ones_normal")}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"]
+
+    def forward(self, x: torch.Tensor, delta: "torch.Tensor | ops.NormedDelta | None" = None,
+                rows: torch.Tensor | None = None, out: torch.Tensor | None = None):
+        if isinstance(delta, torch.Tensor):     # a plain delta: the sum first, then the norm
+            ops.add_(x, delta)
+            delta = None
+        n = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty((n, self.size), dtype=self.weight.dtype, device=x.device)
+        return ops.layernorm(x, self.weight, self.eps, out, delta=delta, rows=rows,
+                             write_stream=delta is not None and rows is None)
+
+    def normed_delta(self, value: torch.Tensor) -> "ops.NormedDelta":
+        """What a sublayer's output becomes when this norm stands between it and the stream."""
+        return ops.NormedDelta(value, self.weight, self.eps)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

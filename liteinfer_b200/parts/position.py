@@ -54,17 +54,46 @@ def rotary_inverse_frequencies(head_dim: int, theta: float, rope_type: str = "de
     return torch.where(~long_wave & ~short_wave, blended, scaled)
 
 
+def yarn_inverse_frequencies(dims: int, theta: float, factor: float, original: float, fast: float,
+                             slow: float) -> tuple[torch.Tensor, float]:
+    """(inv_freq [dims / 2] float32, the factor that multiplies every cosine and sine) of YaRN scaling.
+
+    A pair that turns `t` times within `original` positions has the (fractional) index
+    n(t) = dims * ln(original / (2 pi t)) / (2 ln theta).  Pairs up to lo = floor(n(fast)) keep their frequency
+    f_i = theta^(-2i/dims), pairs from hi = ceil(n(slow)) on have it divided by `factor`, and between them the two
+    are blended linearly in i (lo and hi clamped to [0, dims - 1], a span of at least 0.001).  Cosines and sines
+    are stretched by 0.1 ln(factor) + 1.  Computed in 64-bit, rounded once.
+    """
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    freq = float(theta) ** (-2.0 * i / dims)
+
+    def index_of(turns: float) -> float:
+        return dims * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    blended = freq / factor * ramp + freq * (1.0 - ramp)
+    return blended.to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
 class RotaryEmbedding:
-    """Half-split rotary embedding: dimension j pairs with j + rotary_dim/2 (llama.py:89-102)."""
+    """Half-split rotary embedding: dimension j pairs with j + rotary_dim/2 (llama.py:89-102).  `rope_type`
+    "yarn" takes `factor`, `original_max_position_embeddings`, `fast` and `slow` (`yarn_inverse_frequencies`)."""
 
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rotary_dim: int | None = None, rope_type: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: int = 0) -> None:
+                 original_max_position_embeddings: float = 0, fast: float = 32.0, slow: float = 1.0) -> None:
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
-        inv_freq = rotary_inverse_frequencies(self.rotary_dim, theta, rope_type, factor, low_freq_factor,
-                                              high_freq_factor, original_max_position_embeddings)
-        self.table = RotaryTable(inv_freq.to(device), self.rotary_dim, 1.0)
+        scale = 1.0
+        if rope_type == "yarn":
+            inv_freq, scale = yarn_inverse_frequencies(self.rotary_dim, theta, factor,
+                                                       float(original_max_position_embeddings), fast, slow)
+        else:
+            inv_freq = rotary_inverse_frequencies(self.rotary_dim, theta, rope_type, factor, low_freq_factor,
+                                                  high_freq_factor, int(original_max_position_embeddings))
+        self.table = RotaryTable(inv_freq.to(device), self.rotary_dim, scale)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}

@@ -17,10 +17,11 @@ POSITION_ENCODINGS: dict[str, Callable[..., Any]] = {}
 BLOCKS: dict[str, Callable[..., Any]] = {}
 EMBEDDINGS: dict[str, Callable[..., Any]] = {}
 HEADS: dict[str, Callable[..., Any]] = {}
+REENTRIES: dict[str, Callable[..., Any]] = {}
 
 _TABLES = {
     "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS,
-    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS,
+    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "reentry": REENTRIES,
 }
 
 
@@ -56,6 +57,10 @@ def register_embedding(kind: str, factory, replace: bool = False) -> None:
 
 def register_head(kind: str, factory, replace: bool = False) -> None:
     _register(HEADS, "head", kind, factory, replace)
+
+
+def register_reentry(kind: str, factory, replace: bool = False) -> None:
+    _register(REENTRIES, "re-entry part", kind, factory, replace)
 
 
 def build_part(role: str, spec, **context):

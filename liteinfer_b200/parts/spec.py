@@ -55,16 +55,21 @@ class LayerSpec:
     block: str
     parts: Mapping[str, PartSpec]
     prefixes: Mapping[str, str]
+    # Per role, {the part's own name of a tensor: its name behind the prefix in this checkpoint}, for checkpoints
+    # that spell a tensor differently ("q_proj.weight" stored as "q"); names not listed are kept.
+    renames: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One stop of the forward pass: run `layer`.  `cache_of` is the index of an
     earlier stop of the schedule whose cache this stop reads instead of keeping
-    one of its own (None: its own); such a stop stores nothing."""
+    one of its own (None: its own); such a stop stores nothing.  `reenter`: before this stop the model's
+    `reentry` part runs on the residual stream (with the embedding's output as its second input)."""
 
     layer: int
     cache_of: int | None = None
+    reenter: bool = False
 
 
 @dataclass(frozen=True)
@@ -82,11 +87,26 @@ class ModelSpec:
     # Tensor names that may be absent from a checkpoint because they alias another
     # tensor (a tied head): {absent name: name it reads instead}.
     tied: Mapping[str, str] = field(default_factory=dict)
+    # "float32": the residual stream is kept in 32-bit whatever the engine's dtype (the embedding's output is
+    # widened, the norms read and write it in 32-bit); None: it has the engine's dtype.
+    stream_dtype: str | None = None
+    # A part that mixes the embedding's output back into the stream before the stops marked `reenter`.
+    reentry: PartSpec | None = None
+    reentry_prefix: str = ""
+    # Renames of the tensors of the parts that belong to no layer: {"embedding" | "final_norm" | "head" |
+    # "reentry": {the part's own name: its name behind the prefix}}.
+    renames: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
+    # Checkpoint names that may be present although no part reads them.
+    ignored: tuple[str, ...] = ()
 
     def __post_init__(self) -> None:
         if not self.schedule:
             raise ValueError("a model's schedule names no layer")
+        if self.stream_dtype not in (None, "float32"):
+            raise ValueError(f"stream_dtype {self.stream_dtype!r} is not supported; known: None, 'float32'")
         for stop, entry in enumerate(self.schedule):
+            if entry.reenter and self.reentry is None:
+                raise ValueError(f"stop {stop} re-enters the stream, but the model names no reentry part")
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {entry.layer}, but there are {len(self.layers)}")
             if entry.cache_of is not None:

@@ -37,7 +37,7 @@ def _parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
-    parser.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    parser.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false",
                         help="launch every step kernel by kernel (by default steps are replayed from CUDA graphs, "

@@ -72,7 +72,7 @@ def load_model(model_dir: str | Path, dtype: torch.dtype, device: torch.device |
                 want = expected.get(name)
                 if want is None or name in tied:
                     # A tied head stored beside the embedding is not read (loader.py:64-69 likewise).
-                    if name not in tied and not name.endswith(_IGNORED_SUFFIXES):
+                    if name not in tied and name not in spec.ignored and not name.endswith(_IGNORED_SUFFIXES):
                         unexpected.append(name)
                     continue
                 got = tuple(f.get_slice(name).get_shape())

@@ -1,0 +1,110 @@
+"""Kegizen through the framework's step function, cache manager and engine on a CPU (stand-in kernels), against the
+plain implementation of `plain_kegizen.py`: every way of cutting the same requests gives the same logits."""
+
+from __future__ import annotations
+
+import json
+
+import pytest
+import torch
+
+import kegizen_configs as kc
+import plain_kegizen
+import replay_harness as rh
+
+
+@pytest.fixture(scope="module")
+def kegizen_dirs(tmp_path_factory):
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    base = tmp_path_factory.mktemp("kegizen")
+    return {name: write_random_model(cfg, base / name, seed) for name, (cfg, seed, _) in kc.ALL.items()}
+
+
+def expected_logits(model_dir, requests):
+    config, tensors = plain_kegizen.read_model(model_dir)
+    return {name: plain_kegizen.forward(config, tensors, tokens).float() for name, tokens in requests.items()}
+
+
+def full_trace(requests):
+    trace = rh.Trace()
+    rh.whole(trace, requests)
+    rh.tail_decoded(trace, requests, tail=40)
+    rh.portions(trace, requests)
+    rh.mixed(trace, requests)
+    return trace
+
+
+def test_config_round_trip_and_names(kegizen_dirs):
+    from liteinfer_b200.config.kegizen_config import KegizenConfig
+    from liteinfer_b200.config.registry import resolve
+
+    for name, (raw, _, _) in kc.ALL.items():
+        arch, config = resolve(raw)
+        assert arch.name == "Kegizen" and KegizenConfig.from_dict(config.to_dict()) == config
+        written = json.loads((kegizen_dirs[name] / "config.json").read_text())
+        assert KegizenConfig.from_dict(written) == config
+    arch, config = resolve(kc.KEG_A)
+    spec = arch.build_spec(config)
+    assert [(e.layer, e.reenter) for e in spec.schedule] == [(0, True), (1, False), (0, True), (1, False), (2, False), (3, False)]
+    _, tensors = plain_kegizen.read_model(kegizen_dirs["keg_a"])
+    assert "l3.norm2" not in tensors and "l0.mix.q.norm" in tensors and "l1.mix.q.conv" in tensors and "loop.in" in tensors
+    assert "loop.in" not in plain_kegizen.read_model(kegizen_dirs["keg_b"])[1]
+
+
+@pytest.mark.parametrize("name,lengths", [("keg_a", (1, 7, 61, 90)), ("keg_b", (2, 30, 45)), ("keg_c", (5, 52, 80, 18, 70))])
+def test_all_cuts_match_plain_on_cpu(cpu_kernels, kegizen_dirs, name, lengths):
+    from liteinfer_b200.engine.loading import build_runner
+
+    config, _, page = kc.ALL[name]
+    requests = {f"r{i}": kc.prompt(config["vocab"], n, 100 + i) for i, n in enumerate(lengths)}
+    expected = expected_logits(kegizen_dirs[name], requests)
+    trace = full_trace(requests)
+    assert trace.max_live <= 4
+    runner = build_runner(kegizen_dirs[name], torch.float32, "cpu", page, -(-trace.max_tokens // page), 4)
+    results = rh.run_in_process(runner, trace)
+    worst, where = rh.worst_error(results, rh.gather_expected(trace, expected))
+    assert worst < 5e-5, f"worst difference {worst} at step {where}"
+    assert not runner.cache.live_requests
+    for group in runner.cache.groups:
+        assert group.allocator.num_held == 0
+
+
+def test_window_pages_are_given_back_but_kept_tokens_stay(cpu_kernels, kegizen_dirs):
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.engine.runner import StepEntry
+
+    config, _, page = kc.ALL["keg_c"]                    # window 33, 17 kept tokens, pages of 8
+    runner = build_runner(kegizen_dirs["keg_c"], torch.float32, "cpu", page, 40, 4)
+    tokens = kc.prompt(config["vocab"], 120, 5)
+    runner.step([StepEntry("a", tokens[:100], [])])
+    windowed = [g for g in runner.cache.groups if g.need.window is not None]
+    assert len(windowed) == 1 and windowed[0].need.keep_first == 17
+    table = windowed[0].tables["a"]
+    kept, first = 3, (100 - 33 + 1) // page               # ceil(17 / 8) leading blocks stay; the window starts in block 8
+    assert all(p >= 0 for p in table[:kept]) and all(p < 0 for p in table[kept:first]) and all(p >= 0 for p in table[first:])
+    full = [g for g in runner.cache.groups if g.need.window is None]
+    assert all(p >= 0 for p in full[0].tables["a"])
+    expected = expected_logits(kegizen_dirs["keg_c"], {"a": tokens})["a"]
+    got = runner.step([StepEntry("a", tokens[100:], list(range(20)))])
+    assert float((got - expected[100:]).abs().max()) < 5e-5
+    runner.release("a")
+    runner.cache.check_invariants()
+    assert all(g.allocator.num_held == 0 for g in runner.cache.groups)
+
+
+def test_greedy_generation_through_the_engine(cpu_kernels, kegizen_dirs):
+    """`LLM.generate` (scheduler, sampler, engine loop) on a Kegizen folder picks the plain implementation's tokens."""
+    from liteinfer_b200.engine.llm import LLM
+    from liteinfer_b200.sampling.params import SamplingParams
+
+    config, tensors = plain_kegizen.read_model(kegizen_dirs["keg_a"])
+    prompts = [kc.prompt(config["vocab"], n, 40 + n) for n in (3, 26, 9)]
+    llm = LLM(str(kegizen_dirs["keg_a"]), dtype="float32", device="cpu", block_size=16, num_gpu_blocks=32, max_num_seqs=2,
+              max_model_len=64, max_num_batched_tokens=16, enable_cuda_graphs=False)
+    outputs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+    for prompt, output in zip(prompts, outputs):
+        tokens = list(prompt)
+        for _ in range(6):
+            tokens.append(int(plain_kegizen.forward(config, tensors, tokens)[-1].argmax()))
+        assert list(output.token_ids) == tokens[len(prompt):]

@@ -115,24 +115,25 @@ gemm_simt = linear
 
 
 def rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, heads, kv_heads,
-                  head_dim, rotary_dim, store=True):
+                  head_dim, rotary_dim, store=True, v_head_dim=None, cos_sin_scale=1.0):
     T = qkv.shape[0]
     dtype = qkv.dtype
     page_size = k_pool.shape[2]
+    v_head_dim = head_dim if v_head_dim is None else v_head_dim
     q = qkv[:, :heads * head_dim].float().view(T, heads, head_dim)
     k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].float().view(T, kv_heads, head_dim)
-    v = qkv[:, (heads + kv_heads) * head_dim:].view(T, kv_heads, head_dim)
+    v = qkv[:, (heads + kv_heads) * head_dim:].view(T, kv_heads, v_head_dim)
     if inv_freq is not None and rotary_dim > 0:
         half = rotary_dim // 2
         angle = positions.float()[:, None] * inv_freq.float()[None, :]
-        cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        cos, sin = angle.cos()[:, None, :] * cos_sin_scale, angle.sin()[:, None, :] * cos_sin_scale
 
         def rot(x):
             a, b = x[..., :half], x[..., half:rotary_dim]
             return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., rotary_dim:]), dim=-1)
 
         q, k = rot(q), rot(k)
-    qkv[:, :heads * head_dim] = q.reshape(T, -1).to(dtype)
+        qkv[:, :heads * head_dim] = q.reshape(T, -1).to(dtype)
     if not store:
         return
     # Where each token is written: its slot, from the block tables (tokens of padding belong to no sequence).
@@ -174,8 +175,10 @@ def _runs(seqs, positions):
 
 
 def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens, num_seqs,
-                    max_q_len, heads, kv_heads, head_dim, scale, window=0, plan=None, decode_splits=None):
+                    max_q_len, heads, kv_heads, head_dim, scale, window=0, plan=None, decode_splits=None,
+                    keep_first=0, softcap=0.0):
     dtype = out.dtype
+    v_dim = v_pool.shape[3]
     page_size = k_pool.shape[2]
     groups = heads // kv_heads
     qsl = query_start_loc.tolist()
@@ -185,13 +188,13 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
     slots_of = addressing.slot_table(block_table.tolist()[:num_seqs], [max(c, 0) for c in ctx[:num_seqs]], page_size,
                                      q.device)
     k_flat = k_pool.permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)      # [slot, kv_heads, head_dim]
-    v_flat = v_pool.permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)
+    v_flat = v_pool.permute(0, 2, 1, 3).reshape(-1, kv_heads, v_dim)
     for s in range(num_seqs):
         q0, q1 = qsl[s], qsl[s + 1]
         n, c = q1 - q0, ctx[s]
         if n == 0:
             continue
-        first = 0 if window <= 0 else max(0, (c - n) - window + 1)
+        first = 0 if window <= 0 or keep_first > 0 else max(0, (c - n) - window + 1)
         kpos = torch.arange(first, c, device=q.device)
         slots = slots_of[s, first:c]
         pages = torch.where(slots >= 0, slots // page_size, slots)
@@ -200,17 +203,116 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
         keys = keys.repeat_interleave(groups, dim=1)
         vals = vals.repeat_interleave(groups, dim=1)
         scores = torch.einsum("qhd,khd->hqk", qmat[q0:q1], keys) * scale
+        if softcap > 0:
+            scores = softcap * torch.tanh(scores / softcap)
         qpos = torch.arange(c - n, c, device=q.device)
         hidden = kpos[None, :] > qpos[:, None]
         if window > 0:
-            hidden = hidden | (kpos[None, :] <= qpos[:, None] - window)
+            hidden = hidden | ((kpos[None, :] <= qpos[:, None] - window) & (kpos[None, :] >= keep_first))
         hidden = hidden | (pages < 0)[None, :]
         scores = scores.masked_fill(hidden[None], float("-inf"))
         m = scores.amax(-1, keepdim=True)
         p = torch.exp(scores - m)
         denom = p.sum(-1, keepdim=True)
         o = torch.einsum("hqk,khd->qhd", _r(p, dtype), vals) / denom.permute(1, 0, 2)
-        out[q0:q1] = o.reshape(n, heads * head_dim).to(dtype)
+        out[q0:q1] = o.reshape(n, heads * v_dim).to(dtype)
+    return out
+
+
+def convert(src, dst):
+    dst.copy_(src.to(dst.dtype))
+    return dst
+
+
+def _norm(v, eps, centre=True):
+    if centre:
+        v = v - v.mean(-1, keepdim=True)
+    return v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def layernorm(x, weight, eps, out, delta=None, rows=None, write_stream=False, centre=True):
+    v = (x if rows is None else x[rows.long()]).float()
+    if delta is not None:
+        d = (delta.value if rows is None else delta.value[rows.long()]).float()
+        v = v + delta.weight.float() * _norm(d, delta.eps)
+        if write_stream:
+            x.copy_(v.to(x.dtype))
+            v = x.float()
+    out.copy_((weight.float() * _norm(v, eps, centre)).to(out.dtype))
+    return out
+
+
+def layernorm_add(stream, value, weight, eps):
+    stream.copy_((stream.float() + weight.float() * _norm(value.float(), eps)).to(stream.dtype))
+    return stream
+
+
+def projection_rmsnorm_(x, weight, eps):
+    x.copy_((weight.float() * _norm(x.float(), eps, centre=False)).to(x.dtype))
+    return x
+
+
+def qk_projection_rmsnorm_(q, q_weight, k, k_weight, eps):
+    projection_rmsnorm_(q, q_weight, eps)
+    projection_rmsnorm_(k, k_weight, eps)
+
+
+def gated_rmsnorm(x, gate, weight, eps, out, heads):
+    tokens, width = out.shape
+    size = width // heads
+    g = gate.float()
+    y = _norm(x.view(tokens, heads, size), eps, centre=False) * weight.float()
+    out.copy_((y.reshape(tokens, width) * (g / (1.0 + torch.exp(-g)))).to(out.dtype))
+    return out
+
+
+def short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation="silu"):
+    K = taps.shape[1]
+    qsl, slots = query_start_loc.tolist(), state_slots.tolist()
+    out.zero_()
+    for s in range(len(qsl) - 1):
+        a, b = qsl[s], qsl[s + 1]
+        if b <= a:
+            continue
+        padded = torch.cat([tail[slots[s]].float(), x[a:b].float()])
+        acc = torch.zeros(b - a, x.shape[1], device=x.device)
+        for j in range(K):
+            acc = acc + padded[j:j + b - a] * taps[:, j].float()
+        out[a:b] = (acc / (1.0 + torch.exp(-acc)) if activation == "silu" else acc).to(out.dtype)
+    return out
+
+
+def short_conv_update(x, tail, query_start_loc, state_slots, num_seqs):
+    keep = tail.shape[1]
+    qsl, slots = query_start_loc.tolist(), state_slots.tolist()
+    for s in range(num_seqs):
+        a, b = qsl[s], qsl[s + 1]
+        if b <= a or keep == 0:
+            continue
+        tail[slots[s]] = torch.cat([tail[slots[s]], x[a:b].to(tail.dtype)])[-keep:]
+
+
+def gated_delta_rule(qkv, ab, a_log, dt_bias, state, query_start_loc, state_slots, num_seqs, heads, kv_heads, dim,
+                     vdim, out):
+    qsl, slots = query_start_loc.tolist(), state_slots.tolist()
+    T = qkv.shape[0]
+    qk = kv_heads * dim
+    q = qkv[:, :qk].float().view(T, kv_heads, dim)
+    k = qkv[:, qk:2 * qk].float().view(T, kv_heads, dim)
+    v = qkv[:, 2 * qk:].float().view(T, heads, vdim)
+    q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+    k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+    beta = torch.sigmoid(ab[:, :heads].float())
+    decay = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(ab[:, heads:].float() + dt_bias))
+    for s in range(num_seqs):
+        for t in range(qsl[s], qsl[s + 1]):
+            S = state[slots[s]]
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                S[h] *= decay[t, h]
+                u = beta[t, h] * (v[t, h] - S[h].t() @ k[t, g])
+                S[h] += torch.outer(k[t, g], u)
+                out[t, h * vdim:(h + 1) * vdim] = S[h].t() @ q[t, g]
     return out
 
 
@@ -270,5 +372,6 @@ def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
+ALL = ("convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
+       "short_conv", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
