@@ -300,6 +300,176 @@ def run_ours(args) -> dict:
     }
 
 
+# ---- `--compare kegizen`: the Kegizen decoder beside the Llama decoder at equal layer sizes ----------------------
+def _kegizen_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int) -> dict:
+    """Three delta-rule layers, then one attention layer (a window of 1,024 that keeps 4 tokens, capped scores,
+    YaRN-scaled rotation of all of the head), over and over; every projection as wide as the Llama layer's."""
+    delta = {"type": "delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": heads * head_dim // 128, "kv_heads": heads * head_dim // 128, "dim": 128, "vdim": 128, "conv": 4}}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                           "scale": head_dim ** -0.5, "softcap": 30.0, "mask": {"size": 1024, "keep_first": 4},
+                           "rot": {"dims": head_dim, "base": 10000.0,
+                                   "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Kegizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [attention if i % 4 == 3 else delta for i in range(layers)], "loop": None}
+
+
+def _timed(fn, repeats: int = 20, warmup: int = 5) -> float:
+    """Median milliseconds of `fn()` on the current stream, between CUDA events, after `warmup` calls."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(repeats):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def _kegizen_kernels(peaks: dict) -> dict:
+    """Each kernel of the design alone beside the like kernel of the Llama path, as fractions of the measured copy
+    bandwidth (kernels that stream) or product throughput (attention over prompts).  Inputs are larger than L2
+    where a kernel streams, so every call reads from memory."""
+    import torch
+
+    from liteinfer_b200 import ops
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops_burst"] * 1e12
+    out: dict = {}
+
+    def ints(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    # -- norms over a stream of 16,384 x 2,048 (the 32-bit stream: 134 MB; bfloat16: 67 MB)
+    T, W = 16384, 2048
+    x32, x16 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf)
+    value, w = torch.randn(T, W, device=dev).to(bf), torch.ones(W, dtype=bf, device=dev)
+    normed = torch.empty(T, W, dtype=bf, device=dev)
+    ms = _timed(lambda: ops.layernorm(x32, w, 1e-5, normed, delta=ops.NormedDelta(value, w, 1e-5), write_stream=True))
+    out["layernorm_fused_hbm_frac"] = T * W * (4 + 2 + 4 + 2) / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.rmsnorm(x16, w, 1e-5, normed, delta=value, write_residual=True))
+    out["llama_rmsnorm_fused_hbm_frac"] = T * W * (2 + 2 + 2 + 2) / (ms * 1e-3) / hbm
+
+    # -- short convolutions over 16,384 tokens x 6,144 channels
+    C = 6144
+    xin, taps = torch.randn(T, C, device=dev).to(bf), torch.randn(C, 4, device=dev).to(bf)
+    tail, conved = torch.zeros(4, 3, C, dtype=bf, device=dev), torch.empty(T, C, dtype=bf, device=dev)
+    seq_of, qsl, slots = torch.zeros(T, dtype=torch.int32, device=dev), ints([0, T]), ints([0])
+    ms = _timed(lambda: ops.short_conv(xin, taps, tail, seq_of, qsl, slots, conved))
+    out["short_conv_hbm_frac"] = T * C * 4 / (ms * 1e-3) / hbm
+
+    # -- the recurrence: decode (64 requests x 16 heads x 128 x 128 states: 134 MB read and written) and a prompt
+    H, d = 16, 128
+    for batch, tokens_each, key in ((64, 1, "delta_rule_decode_b64"), (8, 1, "delta_rule_decode_b8"), (1, 2048, "delta_rule_prompt_2048")):
+        n = batch * tokens_each
+        qkv = torch.randn(n, 3 * H * d, device=dev).to(bf)
+        ab = torch.randn(n, 2 * H, device=dev).to(bf)
+        state = torch.zeros(batch, H, d, d, device=dev)
+        read = torch.empty(n, H * d, device=dev)
+        a_log, dt = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        q2 = ints([i * tokens_each for i in range(batch + 1)])
+        sl = ints(list(range(batch)))
+        ms = _timed(lambda: ops.gated_delta_rule(qkv, ab, a_log, dt, state, q2, sl, batch, H, H, d, d, read, tokens_each))
+        out[key + "_us"] = ms * 1e3
+        if tokens_each == 1:
+            out[key + "_hbm_frac"] = batch * H * d * d * 4 * 2 / (ms * 1e-3) / hbm
+        else:
+            out[key + "_us_per_token"] = ms * 1e3 / tokens_each
+
+    # -- attention: a prompt of 2,048 (window 1,024 + 4 kept, capped) on the mma.sync kernel beside the plain
+    #    causal one on the tcgen05 kernel; decode at 64 requests over 1,028 visible keys beside the streaming kernel
+    for head_dim, heads, kv_heads in ((64, 32, 8), (128, 32, 8)):
+        page, n = 16, 2048
+        pages = n // page
+        k_pool = torch.randn(pages * 64, kv_heads, page, head_dim, device=dev).to(bf)
+        v_pool = torch.randn(pages * 64, kv_heads, page, head_dim, device=dev).to(bf)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        q = torch.randn(n, heads * head_dim, device=dev).to(bf)
+        o = torch.empty_like(q)
+        plan = AttentionPlan(num_prefill=1, prefill_seqs=ints([0]), max_prefill_query_len=n)
+        args = (q, q.shape[1], o, k_pool, v_pool, table, ints([0, n]), ints([n]), 1, n, heads, kv_heads, head_dim, head_dim ** -0.5)
+        ms = _timed(lambda: ops.paged_attention(*args, 1024, plan=plan, keep_first=4, softcap=30.0))
+        visible = sum(min(i + 1, 1024 + 4) for i in range(n))
+        out[f"attention_prompt_d{head_dim}_masked_tflops_frac"] = 4 * heads * head_dim * visible / (ms * 1e-3) / tflops
+        out[f"attention_prompt_d{head_dim}_masked_us"] = ms * 1e3
+        ms = _timed(lambda: ops.paged_attention(*args, 0, plan=plan))
+        out[f"llama_attention_prompt_d{head_dim}_tflops_frac"] = 4 * heads * head_dim * n * (n + 1) / 2 / (ms * 1e-3) / tflops
+        out[f"llama_attention_prompt_d{head_dim}_us"] = ms * 1e3
+        B = 64
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages)
+        q = torch.randn(B, heads * head_dim, device=dev).to(bf)
+        o = torch.empty_like(q)
+        plan = AttentionPlan(num_decode=B, decode_seqs=ints(list(range(B))), decode_tokens=ints(list(range(B))),
+                             max_decode_context_len=n)
+        args = (q, q.shape[1], o, k_pool, v_pool, table, ints(list(range(B + 1))), ints([n] * B), B, 1, heads, kv_heads, head_dim, head_dim ** -0.5)
+        ms = _timed(lambda: ops.paged_attention(*args, 1024, plan=plan, keep_first=4, softcap=30.0))
+        out[f"attention_decode_d{head_dim}_masked_hbm_frac"] = B * 1028 * kv_heads * head_dim * 2 * 2 / (ms * 1e-3) / hbm
+        ms = _timed(lambda: ops.paged_attention(*args, 1024, plan=plan))
+        out[f"llama_attention_decode_d{head_dim}_window_hbm_frac"] = B * 1024 * kv_heads * head_dim * 2 * 2 / (ms * 1e-3) / hbm
+    return {k: round(v, 4) for k, v in out.items()}
+
+
+def run_kegizen(args) -> dict:
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 near a context of 2,048) of a Kegizen model
+    and of a Llama model with the same width, depth, head sizes and feed-forward, random weights, bfloat16; and
+    the design's kernels one by one.  Printed as one JSON line; the default run of this file does not include it."""
+    import torch
+
+    from liteinfer_b200 import LLM, SamplingParams
+    from liteinfer_b200.engine.runner import StepEntry
+    from liteinfer_b200.sampling.sampler import Sampler
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    peaks = measured_peaks()
+    steps, warmup, context, vocab = min(args.steps, 32), max(3, min(args.warmup, 8)), 2048, 32000
+    greedy = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True)
+    sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=32, kv_heads=8, head_dim=64),
+             "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
+    result: dict = {"impl": "ours", "compare": "kegizen", "dtype": "bf16", "data": "synthetic ids, random weights",
+                    "peaks": peaks, "models": {}}
+    for name, size in sizes.items():
+        llama = dict(LLAMA_1B, vocab_size=vocab, hidden_size=size["width"], intermediate_size=size["ff"],
+                     num_hidden_layers=size["layers"], num_attention_heads=size["heads"],
+                     num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"], tie_word_embeddings=False)
+        for arch, cfg in (("kegizen", _kegizen_config(vocab=vocab, **size)), ("llama", llama)):
+            with tempfile.TemporaryDirectory() as tmp:
+                model_dir = write_random_model(cfg, Path(tmp) / arch, seed=0)
+                llm = LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=context + 1,
+                          block_size=PAGE, max_num_batched_tokens=8192, gpu_memory_utilization=0.5)
+                runner = llm.engine.runner
+                g = torch.Generator().manual_seed(7)
+                prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+
+                def prefill():
+                    runner.step([StepEntry("prefill", prompt, (PREFILL_TOKENS - 1,))])
+                    runner.release("prefill")
+
+                numbers = {"prefill_2048_ms": round(_timed(prefill, repeats=5, warmup=3), 3)}
+                numbers["prefill_tok_s"] = round(PREFILL_TOKENS / numbers["prefill_2048_ms"] * 1e3)
+                start = context - (warmup + steps) - 1
+                for batch in (8, 64):
+                    rate, ms, launches = _decode_rate(runner, Sampler(0), greedy, batch, start, steps, warmup, vocab)
+                    numbers[f"decode_b{batch}_tok_s"] = round(rate)
+                    numbers[f"decode_b{batch}_ms"] = round(ms, 4)
+                    numbers[f"decode_b{batch}_launches"] = launches
+                numbers["weight_gb"] = round(runner.model.weight_bytes() / 1e9, 3)
+                numbers["decode_b8_weight_hbm_frac"] = round(
+                    runner.model.weight_bytes() / (numbers["decode_b8_ms"] * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+                runner.check_kernels()
+                llm.close()
+                result["models"][f"{name}_{arch}"] = numbers
+    result["kernels"] = _kegizen_kernels(peaks)
+    return result
+
+
 def _shape_numbers(cfg: dict) -> dict:
     layers, hidden, vocab = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["vocab_size"]
     q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
@@ -437,6 +607,9 @@ def main() -> int:
     parser.add_argument("--workload", default="none", choices=["none", "3b", "8b", "all"],
                         help="run the reference's larger configurations instead (64 requests under continuous batching "
                              "at the 3B sizes; decode at a context of 8,192 at the 8B sizes) and print their line")
+    parser.add_argument("--compare", default="none", choices=["none", "kegizen"],
+                        help="instead of the default run: the Kegizen decoder beside the Llama decoder at equal "
+                             "layer sizes (prefill, decode, and the design's kernels one by one)")
     parser.add_argument("--no-workloads", action="store_true",
                         help="leave the 3B and 8B configurations out of the default run (they add about 80 s)")
     args = parser.parse_args()
@@ -444,6 +617,9 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print("liteinfer_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
         return 2
+    if args.compare == "kegizen" and args.impl == "ours":
+        print(json.dumps(run_kegizen(args)))
+        return 0
     if args.workload != "none" and args.impl == "ours":
         print(json.dumps({"impl": "ours", "workloads": run_workloads(args)}))
         return 0

@@ -156,6 +156,22 @@ class CacheManager:
         probe = CacheManager(layer_needs, schedule, page_size, 1, 1, dtype, "cpu", allocate_storage=False)
         return probe.bytes_per_page()
 
+    @staticmethod
+    def state_bytes_for(layer_needs: list[tuple], schedule, max_requests: int, dtype: torch.dtype) -> int:
+        """Bytes of the fixed-size states of `max_requests` slots (every stop that keeps states of its own)."""
+        element = torch.empty((), dtype=dtype).element_size()
+        total = 0
+        for entry in schedule:
+            if entry.cache_of is not None:
+                continue
+            for need in layer_needs[entry.layer]:
+                if isinstance(need, StateNeed):
+                    count = 1
+                    for n in need.shape:
+                        count *= n
+                    total += count * (4 if need.kind == "f32" else element)
+        return total * max_requests
+
     # ----------------------------------------------------------- requests
     def has(self, request_id: str) -> bool:
         return request_id in self._length

@@ -36,7 +36,7 @@ namespace li {
 // is a few instructions per copy; a page size that is a power of two is divided by shifting.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParams& p, const int* table, int kvh,
-                                             int tile_start, int lo, int hi) {
+                                             int tile_start, int lo, int hi, int kept_end = 0) {
   constexpr int kChunks = D / 8;
   constexpr int kKeysPerPass = kWarps * 32 / kChunks;
   const int chunk = threadIdx.x % kChunks, key0 = threadIdx.x / kChunks;
@@ -44,7 +44,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParam
   for (int pass = 0; pass < kBlockN / kKeysPerPass; ++pass) {
     const int key = key0 + pass * kKeysPerPass;
     const int kpos = tile_start + key;
-    bool valid = kpos >= lo && kpos < hi;
+    bool valid = (kpos >= lo || kpos < kept_end) && kpos < hi;
     size_t off = 0;
     if (valid) {
       const int block = p.page_shift >= 0 ? kpos >> p.page_shift : kpos / p.page_size;
@@ -97,9 +97,15 @@ attention_mma_kernel(const AttnParams p) {
   const int hi = last_qpos + 1;
   const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
   const int tile_lo = lo / kBlockN, tile_hi = (hi + kBlockN - 1) / kBlockN;   // key tiles [tile_lo, tile_hi)
-  const int ntiles = tile_hi - tile_lo;
+  // The first keys that stay visible behind the window, [0, kept_end), are walked first: the tiles that hold
+  // them and lie before the window's first tile get the places [place_lo, tile_lo) in front of the window's
+  // tiles, whose place is their own number.  Without kept keys place_lo = tile_lo and a place is a tile.
+  const int kept_end = (p.window > 0 && p.keep_first > 0) ? min(p.keep_first, lo) : 0;
+  const int place_lo = tile_lo - min((kept_end + kBlockN - 1) / kBlockN, tile_lo);
+  const int ntiles = tile_hi - place_lo;
   const int per_split = (ntiles + p.num_splits - 1) / p.num_splits;
-  const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
+  const int my_lo = place_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
+#define LI_TILE_AT(place) ((place) >= tile_lo ? (place) : (place) - place_lo)
 
   const bool fused = kDecode && p.rope_inv_freq != nullptr;
   const int newest_pos = ctx - 1;
@@ -117,7 +123,8 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int st = 0; st < kStages - 1; ++st) {
       if (my_lo + st < my_hi)
-        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh,
+                        LI_TILE_AT(my_lo + st) * kBlockN, lo, hi, kept_end);
       cp_async_commit();
     }
   }
@@ -182,7 +189,8 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int st = 0; st < kStages - 1; ++st) {
       if (my_lo + st < my_hi)
-        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh,
+                        LI_TILE_AT(my_lo + st) * kBlockN, lo, hi, kept_end);
       cp_async_commit();
     }
     cp_async_wait<kStages - 1>();   // the Q tile has landed
@@ -209,14 +217,17 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
-  for (int tile = my_lo; tile < my_hi; ++tile) {
-    const int buf = (tile - my_lo) % kStages;
+  const bool capped = p.cap_out > 0.f;
+  for (int place = my_lo; place < my_hi; ++place) {
+    const int tile = LI_TILE_AT(place);
+    const int buf = (place - my_lo) % kStages;
     bf16* ks = kbuf + buf * kBlockN * D;
     bf16* vs = vbuf + buf * kBlockN * D;
     {
-      const int ahead = tile + kStages - 1, abuf = (ahead - my_lo) % kStages;
+      const int ahead = place + kStages - 1, abuf = (ahead - my_lo) % kStages;
       if (ahead < my_hi)
-        load_kv_tile<D>(kbuf + abuf * kBlockN * D, vbuf + abuf * kBlockN * D, p, table, kvh, ahead * kBlockN, lo, hi);
+        load_kv_tile<D>(kbuf + abuf * kBlockN * D, vbuf + abuf * kBlockN * D, p, table, kvh,
+                        LI_TILE_AT(ahead) * kBlockN, lo, hi, kept_end);
     }
     cp_async_commit();
     cp_async_wait<kStages - 1>();   // all but the newest kStages-1 groups are complete: this tile is here
@@ -258,6 +269,12 @@ attention_mma_kernel(const AttnParams p) {
     // zero queries: their scores are finite, and they are never stored.)
     const bool all_visible = (tile + 1) * kBlockN - 1 <= first_qpos &&
                              (p.window <= 0 || tile * kBlockN > last_qpos - p.window);
+    if (capped) {
+#pragma unroll
+      for (int i = 0; i < kGroupsPerWarp * 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = p.cap_out * fast_tanh(s[i][j] * p.cap_in);   // scaled below like any score
+    }
     if (all_visible) {
 #pragma unroll
       for (int i = 0; i < kGroupsPerWarp * 2; ++i)
@@ -273,7 +290,7 @@ attention_mma_kernel(const AttnParams p) {
         for (int j = 0; j < 4; ++j) {
           const int kpos = key0 + i * 8 + 2 * t + (j & 1);
           const int qp = qpos[j >> 1];
-          const bool visible = kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+          const bool visible = kpos <= qp && (p.window <= 0 || kpos > qp - p.window || kpos < p.keep_first);
           s[i][j] = visible ? s[i][j] * p.scale_log2 : -INFINITY;
           tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[i][j]);
         }
@@ -439,6 +456,8 @@ LI_EXPORT int li_paged_attention_mma_decode_capacity(int head_dim) {
 }
 
 // Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups of at most 64 heads).
+// keep_first (with a window): the first keys of a sequence stay visible behind the window.  softcap > 0: a scaled
+// score s becomes softcap * tanh(s / softcap).  Neither goes with rope_inv_freq.
 // seq_index (optional, [num_seqs]): the batch rows to run, so that a mixed step can send its
 // single-token sequences through a split launch and the others through an unsplit one.
 // num_splits > 1 needs scratch: partial_out [tokens*heads*splits, head_dim] and partial_lse
@@ -457,8 +476,10 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
                                      int head_dim, int page_size, int num_pages, float scale, int window,
                                      int num_splits, float* partial_out, float* partial_lse, unsigned* counters,
                                      const float* rope_inv_freq, const void* k_new, const void* v_new, int store_new,
-                                     cudaStream_t stream) {
+                                     int keep_first, float softcap, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (rope_inv_freq && (keep_first > 0 || softcap > 0.f)) return LI_ERR_UNSUPPORTED;
+  if (scale == 0.f) return LI_ERR_UNSUPPORTED;
   if (kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
   const int groups = heads / kv_heads;
   if (groups > kBlockM || (head_dim != 64 && head_dim != 128)) return LI_ERR_UNSUPPORTED;
@@ -474,6 +495,9 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
   if ((page_size & (page_size - 1)) == 0)
     for (int s = 0; s < 31; ++s)
       if ((1 << s) == page_size) p.page_shift = s;
+  p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+  p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
   const bool decode = max_q_len == 1 && groups <= 16;
   if (rope_inv_freq && (!decode || !k_new || !v_new || !aligned16(k_new) || !aligned16(v_new))) return LI_ERR_UNSUPPORTED;
   if (!decode)

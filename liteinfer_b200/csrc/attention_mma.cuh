@@ -39,6 +39,11 @@ struct AttnParams {
   int* error_flag;              // kernels with bounded waits record here where one gave up (may be null)
   int cluster_merge;            // the splits of a (sequence, KV head) are one thread-block cluster and merge through
                                 // distributed shared memory (attention_stream.cu only)
+  // attention_mma.cu only.  With a window, the first keep_first keys of a sequence stay visible behind it.  A
+  // score s (unscaled) becomes cap_out * tanh(s * cap_in) when cap_out > 0, and is then scaled like any other:
+  // cap_in = scale / cap, cap_out = cap / scale.
+  int keep_first;
+  float cap_in, cap_out;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -69,6 +74,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// tanh(x) = 1 - 2 / (1 + e^(2x)) from one exponential and one division: exact at both ends (the exponential
+// overflows to infinity or flushes to zero), an absolute error of a few 1e-7 in between.
+__device__ __forceinline__ float fast_tanh(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390082f));
+  return 1.f - __fdividef(2.f, 1.f + e);
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

@@ -76,6 +76,118 @@ layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __rest
   for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<T>((row[c] - mean) * inv * to_float(weight[c]));
 }
 
+// Four neighbouring elements as floats, by one 16-byte (float) or 8-byte (bfloat16) access.
+__device__ __forceinline__ void load4(const float* p, float (&o)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&o)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&a);
+  raw.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same norm with the row in registers: thread i keeps the four-element chunks i, i + blockDim, ... (NV of them).
+// For widths that are multiples of four and at most 4 * NV * blockDim, and 16-byte aligned rows.
+template <typename T, typename X, int NV>
+__global__ void __launch_bounds__(1024)
+layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __restrict__ value_weight,
+                      const T* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width,
+                      float eps, float value_eps, int write_stream, int centre) {
+  __shared__ float scratch[33];
+  // The weights are inputs of the model, not of a kernel: they are on their way before the wait.
+  float w[NV][4], wd[NV][4];
+  int col[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    col[i] = (i * blockDim.x + threadIdx.x) * 4;
+    if (col[i] < width) {
+      if (weight != nullptr) load4(weight + col[i], w[i]);
+      if (value != nullptr) load4(value_weight + col[i], wd[i]);
+    }
+  }
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const size_t at = (size_t)(rows ? rows[r] : r) * width;
+  const float n = (float)width;
+  float v[NV][4];
+  if (value != nullptr) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (col[i] < width) {
+        load4(value + at + col[i], v[i]);
+        s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
+      }
+    }
+    const float mean = block_sum(s, scratch) / n;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (col[i] < width)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[i][e] -= mean;
+          q = fmaf(v[i][e], v[i][e], q);
+        }
+    const float inv = 1.0f / sqrtf(block_sum(q, scratch) / n + value_eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (col[i] < width) {
+        float base[4];
+        load4(x + at + col[i], base);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[i][e] = base[e] + v[i][e] * inv * wd[i][e];
+        if (write_stream) store4(x + at + col[i], v[i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[i][e] = round_to<X>(v[i][e]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (col[i] < width) load4(x + at + col[i], v[i]);
+  }
+  if (out == nullptr) return;
+  float mean = 0.f;
+  if (centre) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (col[i] < width) s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
+    mean = block_sum(s, scratch) / n;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+    if (col[i] < width)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[i][e] -= mean;
+        q = fmaf(v[i][e], v[i][e], q);
+      }
+  const float inv = 1.0f / sqrtf(block_sum(q, scratch) / n + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (col[i] < width) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[i][e] = v[i][e] * inv * w[i][e];
+      store4(out + (size_t)r * width + col[i], v[i]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024)
 projection_rmsnorm_kernel(T* __restrict__ x, size_t stride, int width_a, const T* __restrict__ weight_a, int width_b,
@@ -152,6 +264,29 @@ LI_EXPORT int li_layernorm(int dtype, void* x, int x_dtype, const void* value, c
   const size_t smem = (size_t)width * sizeof(float);
   const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
   const int write_stream = flags & 1, centre = (flags & 2) ? 0 : 1;
+  // Rows of up to 16,384 elements that 16-byte accesses can walk stay in registers.
+  const bool in_registers = width % 4 == 0 && width <= 16384 && aligned16(x) && aligned16(value) && aligned16(out) &&
+                            aligned16(weight) && aligned16(value_weight);
+  if (in_registers) {
+    const int quads = width / 4;
+    const int block = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
+    const int per_thread = (quads + block - 1) / block;
+#define LI_LAUNCH_ROWS(T, X, NV)                                                                                      \
+  return (int)launch_pdl(n, layernorm_rows_kernel<T, X, NV>, dim3(n), dim3(block), 0, stream, (X*)x, (const T*)value,  \
+                         (const T*)value_weight, (const T*)weight, (T*)out, rows, width, eps, value_eps, write_stream, \
+                         centre)
+#define LI_LAUNCH_ROWS_NV(T, X)                                                                                       \
+  {                                                                                                                   \
+    if (per_thread == 1) LI_LAUNCH_ROWS(T, X, 1);                                                                     \
+    if (per_thread == 2) LI_LAUNCH_ROWS(T, X, 2);                                                                     \
+    LI_LAUNCH_ROWS(T, X, 4);                                                                                          \
+  }
+    if (dtype == kFloat32) LI_LAUNCH_ROWS_NV(float, float)
+    if (x_dtype == kFloat32) LI_LAUNCH_ROWS_NV(bf16, float)
+    LI_LAUNCH_ROWS_NV(bf16, bf16)
+#undef LI_LAUNCH_ROWS_NV
+#undef LI_LAUNCH_ROWS
+  }
 #define LI_LAUNCH_NORM(T, X)                                                                                          \
   {                                                                                                                   \
     if (smem > 48 * 1024) {                                                                                           \

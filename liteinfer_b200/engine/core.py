@@ -135,7 +135,8 @@ class EngineCore:
         element = torch.empty((), dtype=cfg.dtype).element_size()
         widest = min(cfg.token_budget, cfg.max_num_seqs * cfg.max_model_len)
         activations = widest * model.spec.hidden_size * element * 32 + cfg.max_num_seqs * model.spec.vocab_size * 8
-        budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - activations
+        states = CacheManager.state_bytes_for(model.cache_needs(), model.schedule, cfg.max_num_seqs, cfg.dtype)
+        budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - activations - states
         affordable = max(0, budget // per_page)
         if affordable < reachable:
             servable = affordable * cfg.block_size // max(1, cfg.max_model_len)

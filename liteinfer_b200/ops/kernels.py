@@ -54,16 +54,16 @@ _SIGNATURES = {
     "li_gated_rmsnorm": ("layernorm", [c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int,
                                        c_float, c_void_p]),
     "li_short_conv": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "li_short_conv_update": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_void_p]),
     "li_gated_delta_rule": ("delta_rule", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int, c_void_p]),
+                                           c_void_p, c_void_p]),
     "li_paged_attention_mma": ("attention_mma", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "li_paged_attention_stream": ("attention_stream", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -709,12 +709,13 @@ def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, q
 
 def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                         seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0,
-                        num_splits=1, newest=None, streaming=False) -> torch.Tensor:
+                        num_splits=1, newest=None, streaming=False, keep_first=0, softcap=0.0) -> torch.Tensor:
     """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys
     over that many blocks, the last of which merges the partial results.  `newest` (NewestToken, single-token
     sequences only): q is unrotated and the newest key and value are not in their pages yet; the kernel
     rotates q and the key and stores key and value itself.  `streaming` (single-token sequences, sizes that
-    `stream_attention_supports` allows): the kernel that passes K and V through registers only."""
+    `stream_attention_supports` allows): the kernel that passes K and V through registers only.  `keep_first`
+    (with a window) and `softcap`: as in `paged_attention`; not with `newest` or `streaming`."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape
     partial_out = partial_lse = counters = None
@@ -729,7 +730,7 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
     tail = (_ptr(newest.inv_freq if newest else None), _ptr(newest.k if newest else None),
             _ptr(newest.v if newest else None), int(newest.store) if newest else 0)
     if streaming:
-        assert max_q_len == 1
+        assert max_q_len == 1 and keep_first <= 0 and softcap <= 0
         _check(_fn("li_paged_attention_stream")(
             q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
             block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
@@ -741,7 +742,8 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail, _stream()),
+        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail, int(keep_first),
+        float(softcap), _stream()),
         "paged_attention_mma")
     return out
 
@@ -819,26 +821,31 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     assert (kvh, hd) == (kv_heads, head_dim) and q.dtype == out.dtype == k_pool.dtype == v_pool.dtype
     if newest is not None and not fused_decode_supports(q.dtype, heads, kv_heads, head_dim, head_dim, plan):
         raise ValueError("the decode kernel with the rotary encoding fused in does not take this step")
-    plain = softcap <= 0 and (keep_first <= 0 or window <= 0) and v_pool.shape[3] == head_dim
-    if not plain or not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
+    masked = softcap > 0 or (keep_first > 0 and window > 0)
+    if v_pool.shape[3] != head_dim or not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
         assert newest is None
         return paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc,
                                        context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
                                        keep_first, softcap)
     common = (q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
+    # Kept first keys and capped scores are options of the mma.sync kernel only (prompts and single tokens alike).
+    options = dict(keep_first=keep_first, softcap=softcap) if masked else {}
     if plan is None:
-        return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
+        return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
+                                   **options)
     if plan.num_prefill:
-        many = (paged_attention_tcgen05 if tcgen05_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size)
-                else paged_attention_mma)
-        many(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads, kv_heads, head_dim,
-             scale, window)
+        if not masked and tcgen05_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size):
+            paged_attention_tcgen05(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
+                                    kv_heads, head_dim, scale, window)
+        else:
+            paged_attention_mma(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
+                                kv_heads, head_dim, scale, window, **options)
     if plan.num_decode:
-        bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
-        streaming = stream_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size)
+        bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window + keep_first)
+        streaming = not masked and stream_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size)
         splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound, head_dim, streaming)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
-                            window, splits, newest, streaming)
+                            window, splits, newest, streaming, **options)
     return out
 
 
@@ -946,15 +953,31 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     return out
 
 
+def short_conv_step(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_token: torch.Tensor,
+                    query_start_loc: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, out: torch.Tensor,
+                    activation: str = "silu", single_tokens: bool = False) -> torch.Tensor:
+    """`short_conv`, then `short_conv_update`: a step's convolution and the tails moved on by it.  With
+    `single_tokens` (every sequence of the step brings exactly one token) one launch does both where the kernel
+    can."""
+    if single_tokens and short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation,
+                                    move_tail=True) is not None:
+        return out
+    short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation)
+    short_conv_update(x, tail, query_start_loc, state_slots, num_seqs)
+    return out
+
+
 def short_conv(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_token: torch.Tensor,
                query_start_loc: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
-               activation: str = "silu") -> torch.Tensor:
+               activation: str = "silu", move_tail: bool = False) -> "torch.Tensor | None":
     """A short causal convolution over time per channel, then the activation.
 
     x [tokens, channels] (a column slice is fine): this step's inputs, every sequence's end to end.  taps
     [channels, K]: column K-1 multiplies the current token, K-2 the one before.  tail [slots, K-1, channels]: the
     last K-1 inputs of each request before this step (zeros at its start), oldest first; it is read, not written
-    (`short_conv_update` moves it on).  Tokens whose sequence is -1 give zeros."""
+    (`short_conv_update` moves it on).  Tokens whose sequence is -1 give zeros.  `move_tail` (only for steps in
+    which every sequence brings exactly one token): the launch also moves the tails on; None is returned, and
+    nothing done, where the kernel cannot (sizes that its vector form does not take)."""
     _rows2d(x, "x")
     _on_gpu(taps, tail, seq_of_token, query_start_loc, state_slots, out)
     _int32(seq_of_token, "seq_of_token"); _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
@@ -964,10 +987,13 @@ def short_conv(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_t
     assert tail.shape[1:] == (K - 1, channels) and tail.dtype == x.dtype
     if activation not in ("silu", "none"):
         raise KernelLibraryError(f"short_conv knows the activations 'silu' and 'none', not {activation!r}")
-    _check(_fn("li_short_conv")(_code(x), x.data_ptr(), x.stride(0), taps.data_ptr(), tail.data_ptr() if K > 1 else None,
+    code = _fn("li_short_conv")(_code(x), x.data_ptr(), x.stride(0), taps.data_ptr(), tail.data_ptr() if K > 1 else None,
                                 seq_of_token.data_ptr(), query_start_loc.data_ptr(), state_slots.data_ptr(),
-                                out.data_ptr(), tokens, channels, K, 1 if activation == "silu" else 0, _stream()),
-           "short_conv")
+                                out.data_ptr(), tokens, channels, K, 1 if activation == "silu" else 0,
+                                int(move_tail and K > 1), _stream())
+    if move_tail and code == 100001:
+        return None
+    _check(code, "short_conv")
     return out
 
 
@@ -988,7 +1014,8 @@ def short_conv_update(x: torch.Tensor, tail: torch.Tensor, query_start_loc: torc
 
 def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                      state: torch.Tensor, query_start_loc: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
-                     heads: int, kv_heads: int, dim: int, vdim: int, out: torch.Tensor) -> torch.Tensor:
+                     heads: int, kv_heads: int, dim: int, vdim: int, out: torch.Tensor,
+                     max_query_len: int = 0) -> torch.Tensor:
     """The gated delta rule, token by token, on a 32-bit state per request and head.
 
     qkv [tokens, 2 * kv_heads * dim + heads * vdim]: q and k (kv_heads heads of dim; head h of the values reads
@@ -996,19 +1023,26 @@ def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, d
     fine) [tokens, 2 * heads]: per head the raw write strength (beta = sigmoid) and, behind those, the raw decay
     input (g = exp(-exp(a_log) * softplus(raw + dt_bias))).  q and k are made unit vectors (x / sqrt(sum x^2 +
     1e-6)), q also times dim^-0.5.  Per token: S *= g; u = beta * (v - S^T k); S += k u^T; o = S^T q.
-    state [slots, heads, dim, vdim] float32 is read and written; out [tokens, heads * vdim] float32."""
+    state [slots, heads, vdim, dim] float32 (S kept column by column) is read and written; out [tokens, heads *
+    vdim] float32.  `max_query_len`: the most tokens a sequence brings, if known (1 picks the variant for steps
+    of single tokens)."""
     _on_gpu(qkv, a_log, dt_bias, state, query_start_loc, state_slots, out)
     _rows2d(ab, "ab")
     _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
     tokens = qkv.shape[0]
     assert qkv.shape[1] == 2 * kv_heads * dim + heads * vdim and ab.shape == (tokens, 2 * heads) and ab.dtype == qkv.dtype
     assert a_log.dtype == dt_bias.dtype == state.dtype == out.dtype == torch.float32
-    assert a_log.numel() == dt_bias.numel() == heads and state.shape[1:] == (heads, dim, vdim)
+    assert a_log.numel() == dt_bias.numel() == heads and state.shape[1:] == (heads, vdim, dim)
     assert out.shape == (tokens, heads * vdim) and heads % kv_heads == 0
+    # What the kernel in front leaves for the recurrence: per token the unit-norm scales and the gates.
+    scratch = torch.empty(2 * max(tokens, 1) * (kv_heads + heads), dtype=torch.float32, device=qkv.device)
     _check(_fn("li_gated_delta_rule")(_code(qkv), qkv.data_ptr(), ab.data_ptr(), ab.stride(0), tokens, num_seqs,
                                       a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), query_start_loc.data_ptr(),
-                                      state_slots.data_ptr(), out.data_ptr(), heads, kv_heads, dim, vdim, 0, 0,
-                                      _stream()), "gated_delta_rule")
+                                      state_slots.data_ptr(), out.data_ptr(), heads, kv_heads, dim, vdim,
+                                      int(max_query_len), scratch.data_ptr(), _stream()), "gated_delta_rule")
+    if max_query_len != 1:
+        global launch_count
+        launch_count += 1   # two kernels
     return out
 
 

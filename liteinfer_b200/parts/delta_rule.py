@@ -72,7 +72,7 @@ class GatedDeltaRule:
         self.norm_weight, self.o_weight = tensors["norm.weight"].contiguous(), tensors["o_proj.weight"]
 
     def cache_needs(self) -> tuple:
-        return (StateNeed((self.heads, self.dim, self.vdim), "f32", name=self.state_name),
+        return (StateNeed((self.heads, self.vdim, self.dim), "f32", name=self.state_name),     # S^T: column by column
                 StateNeed((self.taps - 1, self.channels), "weight", name=self.tail_name))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
@@ -83,13 +83,12 @@ class GatedDeltaRule:
         proj = ops.linear(x, self.in_weight, None)
         c, v = self.channels, self.v_width
         conved = torch.empty((tokens, c), dtype=x.dtype, device=x.device)
-        ops.short_conv(proj[:, :c], self.conv_weight, tail, ctx.seq_of_token, ctx.query_start_loc, ctx.state_slots,
-                       conved, "silu")
-        ops.short_conv_update(proj[:, :c], tail, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs)
+        ops.short_conv_step(proj[:, :c], self.conv_weight, tail, ctx.seq_of_token, ctx.query_start_loc, ctx.state_slots,
+                            ctx.num_seqs, conved, "silu", single_tokens=ctx.max_query_len == 1)
         read = torch.empty((tokens, v), dtype=torch.float32, device=x.device)
         ops.gated_delta_rule(conved, proj[:, c + v:c + v + 2 * self.heads], self.a_log, self.dt_bias, state,
                              ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, self.heads, self.kv_heads, self.dim,
-                             self.vdim, read)
+                             self.vdim, read, ctx.max_query_len)
         gated = torch.empty((tokens, v), dtype=x.dtype, device=x.device)
         ops.gated_rmsnorm(read, proj[:, c:c + v], self.norm_weight, self.norm_eps, gated, self.heads)
         return ops.linear(gated, self.o_weight, None)

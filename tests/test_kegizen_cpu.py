@@ -108,3 +108,31 @@ def test_greedy_generation_through_the_engine(cpu_kernels, kegizen_dirs):
         for _ in range(6):
             tokens.append(int(plain_kegizen.forward(config, tensors, tokens)[-1].argmax()))
         assert list(output.token_ids) == tokens[len(prompt):]
+
+
+def test_cache_manager_kept_tokens_and_value_size():
+    """A window that keeps first tokens costs their pages on top of the window's; values of another size than keys
+    get a pool of their own; such needs group apart from plain ones."""
+    from liteinfer_b200.cache.manager import CacheManager
+    from liteinfer_b200.parts.context import KVNeed
+    from liteinfer_b200.parts.spec import ScheduleEntry
+
+    needs = [(KVNeed(2, 16, 24, v_head_dim=40, keep_first=9),), (KVNeed(2, 16, 24),), (KVNeed(2, 16, 24, v_head_dim=40, keep_first=9),)]
+    m = CacheManager(needs, tuple(ScheduleEntry(i) for i in range(3)), 8, 32, 4, torch.float32, "cpu")
+    assert len(m.groups) == 2
+    kept, plain = m.groups
+    assert kept.pool.shape == (2, 1, 32, 2, 8, 16) and kept.v_pool.shape == (2, 32, 2, 8, 40) and plain.v_pool is None
+    caches = m.layer_caches()
+    assert caches[0].kv.v_pool.shape == (32, 2, 8, 40) and caches[1].kv.v_pool.shape == (32, 2, 8, 16)
+    assert caches[2].kv.k_pool.data_ptr() != caches[0].kv.k_pool.data_ptr()
+    assert kept.kept_blocks == 2 and plain.kept_blocks == 0
+    assert kept.pages_at(200, 1) == plain.pages_at(200, 1) + 2 and kept.pages_at(10, 10) == 2
+    m.reserve(["a"], [100])
+    m.commit("a", 100)
+    first = (100 - 24 + 1) // 8
+    assert [p >= 0 for p in kept.tables["a"]] == [True, True] + [False] * (first - 2) + [True] * (13 - first)
+    assert [p >= 0 for p in plain.tables["a"]] == [False] * first + [True] * (13 - first)
+    assert m.bytes_per_page() == 4 * 8 * 2 * (2 * (16 + 40) + (16 + 16))
+    m.release("a")
+    m.check_invariants()
+    assert kept.allocator.num_held == 0 and plain.allocator.num_held == 0

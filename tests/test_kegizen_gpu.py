@@ -44,7 +44,7 @@ def test_convert_between_column_slices(src, dst):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [48, 257, 2048])
+@pytest.mark.parametrize("width", [48, 257, 2048, 8192, 12288, 20000])
 def test_layernorm_alone_with_delta_and_rows(dtype, width):
     from liteinfer_b200 import ops
 
@@ -129,26 +129,29 @@ def test_short_conv_in_portions_equals_whole(dtype, taps):
     slots that are not in order; the twin agrees."""
     from liteinfer_b200 import ops
 
-    channels, lengths, slots = 70, (23, 9), _ints([5, 2])
-    x = [_randn(n, channels + 6, seed=10 + i, dtype=dtype) for i, n in enumerate(lengths)]
+    channels, lengths, slots = (72 if taps != 2 else 70), (23, 9), _ints([5, 2])       # 72: the vector kernels' sizes
+    x = [_randn(n, channels + 8, seed=10 + i, dtype=dtype) for i, n in enumerate(lengths)]
     w = _randn(channels, taps, seed=3, scale=0.5, dtype=dtype)
 
     def run(impl, cuts):
         tail = torch.zeros(8, taps - 1, channels, dtype=dtype, device=DEV)
         outs = [[] for _ in lengths]
         for step in _cut(lengths, cuts):
-            rows = torch.cat([x[i][a:b] for i, (a, b) in enumerate(step)])[:, 3:3 + channels]
+            rows = torch.cat([x[i][a:b] for i, (a, b) in enumerate(step)])[:, 8:8 + channels]
             counts = [b - a for a, b in step]
             qsl = _ints([0, counts[0], counts[0] + counts[1]])
             seq_of = _ints([0] * counts[0] + [1] * counts[1])
             out = torch.empty(rows.shape[0], channels, dtype=dtype, device=DEV)
-            impl.short_conv(rows, w, tail, seq_of, qsl, slots, out, "silu")
-            impl.short_conv_update(rows, tail, qsl, slots, 2)
+            if max(counts) == 1 and min(counts) == 1:      # the step function's call: one launch where the kernel can
+                impl.short_conv_step(rows, w, tail, seq_of, qsl, slots, 2, out, "silu", single_tokens=True)
+            else:
+                impl.short_conv(rows, w, tail, seq_of, qsl, slots, out, "silu")
+                impl.short_conv_update(rows, tail, qsl, slots, 2)
             outs[0].append(out[:counts[0]]); outs[1].append(out[counts[0]:])
         return [torch.cat(o) for o in outs], tail
 
     whole, tail_whole = run(ops, [lengths])
-    cuts = [(1, 2), (2, 1), (1, 1), (5, 1), (2, 2), (12, 2)]
+    cuts = [(1, 2), (2, 1), (1, 1), (1, 1), (1, 1), (3, 1), (2, 1), (12, 1)]
     parts, tail_parts = run(ops, cuts)
     want, tail_want = run(ref, cuts)
     for a, b, c in zip(whole, parts, want):
@@ -173,7 +176,8 @@ def test_short_conv_skips_padding():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 24, 16), (3, 3, 48, 20), (2, 1, 128, 40), (6, 2, 8, 72), (1, 1, 200, 33)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 24, 16), (3, 3, 48, 20), (2, 1, 128, 40), (6, 2, 8, 72), (1, 1, 200, 33),
+                                                      (2, 2, 64, 32), (1, 1, 256, 8), (2, 1, 32, 36)])
 def test_gated_delta_rule_in_portions_equals_whole(dtype, heads, kv_heads, dim, vdim):
     from liteinfer_b200 import ops
 
@@ -184,7 +188,7 @@ def test_gated_delta_rule_in_portions_equals_whole(dtype, heads, kv_heads, dim, 
     a_log, dt_bias = torch.log(1 + 3 * torch.rand(heads, device=DEV)), _randn(heads, seed=5)
 
     def run(impl, cuts):
-        state = torch.zeros(4, heads, dim, vdim, device=DEV)
+        state = torch.zeros(4, heads, vdim, dim, device=DEV)
         outs = [[] for _ in lengths]
         for step in _cut(lengths, cuts):
             rows = torch.cat([qkv[i][a:b] for i, (a, b) in enumerate(step)])
@@ -192,18 +196,19 @@ def test_gated_delta_rule_in_portions_equals_whole(dtype, heads, kv_heads, dim, 
             counts = [b - a for a, b in step]
             qsl = _ints([0, counts[0], counts[0] + counts[1]])
             out = torch.zeros(rows.shape[0], heads * vdim, device=DEV)
-            impl.gated_delta_rule(rows, gates, a_log, dt_bias, state, qsl, slots, 2, heads, kv_heads, dim, vdim, out)
+            impl.gated_delta_rule(rows, gates, a_log, dt_bias, state, qsl, slots, 2, heads, kv_heads, dim, vdim, out,
+                                  max(counts))
             outs[0].append(out[:counts[0]]); outs[1].append(out[counts[0]:])
         return [torch.cat(o) for o in outs], state
 
     whole, state_whole = run(ops, [lengths])
-    cuts = [(2, 1), (1, 1), (1, 0), (7, 1), (8, 3)]
+    cuts = [(2, 1), (1, 1), (1, 0), (1, 1), (6, 0), (8, 3)]      # steps of single tokens take the kernel's other variant
     parts, state_parts = run(ops, cuts)
     want, state_want = run(ref, cuts)
     for a, b, c in zip(whole, parts, want):
-        assert torch.equal(a, b)                                          # the same chain however it is cut
+        torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-7)            # the same chain however it is cut
         torch.testing.assert_close(a, c, rtol=1e-4, atol=1e-5)
-    assert torch.equal(state_whole, state_parts)
+    torch.testing.assert_close(state_whole, state_parts, rtol=1e-6, atol=1e-7)
     torch.testing.assert_close(state_parts, state_want, rtol=1e-4, atol=1e-5)
     assert not state_parts[[1, 2]].any()
 
@@ -223,7 +228,7 @@ def test_gated_delta_rule_recalls_a_far_key():
     ab[:, 0] = 30.0                                            # beta = 1
     for decay_raw, factor in ((-60.0, 1.0), (0.0, None)):
         ab[:, 1] = decay_raw
-        state = torch.zeros(1, 1, dim, vdim, device=DEV)
+        state = torch.zeros(1, 1, vdim, dim, device=DEV)
         out = torch.zeros(n, vdim, device=DEV)
         ops.gated_delta_rule(qkv, ab, torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), state, _ints([0, n]),
                              _ints([0]), 1, 1, 1, dim, vdim, out)
@@ -293,6 +298,60 @@ def test_attention_edges_of_window_and_kept_tokens_stand_out(decode):
         assert close == seen, f"key {key} for the query at {pos}: expected {'visible' if seen else 'hidden'}"
 
 
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("window,keep_first,softcap", [(100, 4, 20.0), (70, 0, 8.0), (64, 130, 0.0), (0, 0, 15.0), (200, 65, 30.0)])
+def test_tensor_core_attention_with_kept_tokens_and_softcap(head_dim, window, keep_first, softcap):
+    """The mma.sync kernel's options (prompts, portions and split single tokens) against the plain function."""
+    from liteinfer_b200 import ops
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    heads, kv_heads, page, dtype = 4, 2, 16, torch.bfloat16
+    lengths, queries = (333, 700, 1, 260, 515), (333, 1, 1, 7, 1)
+    case = _paged_case(lengths, queries, kv_heads, head_dim, head_dim, page, dtype, seed=3)
+    q = _randn(case.tokens, heads * head_dim, seed=9, dtype=dtype)
+    out, want = (torch.zeros(case.tokens, heads * head_dim, dtype=dtype, device=DEV) for _ in range(2))
+    args = (case.k_pool, case.v_pool, case.table, case.qsl, case.ctx, 5, 333, heads, kv_heads, head_dim, head_dim ** -0.5, window)
+    ref.paged_attention(q, q.shape[1], want, *args, keep_first=keep_first, softcap=softcap)
+    ops.paged_attention(q, q.shape[1], out, *args, keep_first=keep_first, softcap=softcap)
+    torch.testing.assert_close(out.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
+    plan = AttentionPlan(num_decode=3, decode_seqs=_ints([1, 2, 4]), decode_tokens=_ints([333, 334, 342]), num_prefill=2,
+                         prefill_seqs=_ints([0, 3]), max_prefill_query_len=333, max_decode_context_len=700)
+    for splits in (None, 3):
+        out.zero_()
+        ops.paged_attention(q, q.shape[1], out, *args, plan=plan, decode_splits=splits, keep_first=keep_first, softcap=softcap)
+        torch.testing.assert_close(out.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_tensor_core_attention_edges_stand_out(decode):
+    """As `test_attention_edges_of_window_and_kept_tokens_stand_out`, on the mma.sync kernel (bfloat16, head 64),
+    with edges inside a key tile and on a tile's border."""
+    from liteinfer_b200 import ops
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    head_dim, page, n, dtype = 64, 16, 400, torch.bfloat16
+    for window, keep in ((143, 5), (128, 64), (208, 70)):
+        case = _paged_case((n,), (1 if decode else n,), 1, head_dim, head_dim, page, dtype, seed=4)
+        case.k_pool.mul_(0.01)
+        pos = n - 1
+        plan = (AttentionPlan(num_decode=1, decode_seqs=_ints([0]), decode_tokens=_ints([0]), max_decode_context_len=n)
+                if decode else None)
+        for key, seen in ((pos - window + 1, True), (pos - window, False), (keep - 1, True), (keep, False), (0, True)):
+            k_pool = case.k_pool.clone()
+            slot = int(case.table[0, key // page])
+            k_pool[slot, 0, key % page] = 0.0
+            k_pool[slot, 0, key % page, 2] = 60.0
+            q = torch.zeros(case.tokens, head_dim, dtype=dtype, device=DEV)
+            q[:, 2] = 1.0
+            out = torch.zeros(case.tokens, head_dim, dtype=dtype, device=DEV)
+            ops.paged_attention(q, head_dim, out, k_pool, case.v_pool, case.table, case.qsl, case.ctx, 1, case.tokens, 1, 1,
+                                head_dim, 1.0, window, plan=plan, decode_splits=2 if decode else None, keep_first=keep,
+                                softcap=0.0)
+            value = case.v_pool[slot, 0, key % page]
+            close = float((out[-1].float() - value.float()).abs().max()) < 2e-2
+            assert close == seen, f"window {window}, kept {keep}: key {key} for the query at {pos}"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_rope_kv_write_partial_rotation_scaled_and_wide_values(dtype):
     from liteinfer_b200 import ops
@@ -360,8 +419,8 @@ def test_layers_one_by_one_against_plain(kegizen_dirs):
     want: list = []
     plain_kegizen.forward(config, tensors, tokens, want)
     runner = build_runner(kegizen_dirs["keg_a"], torch.float32, DEV, 16, 8, 2)
-    context = runner.build_context([StepEntry("a", tokens, [44])])
     runner.cache.reserve(["a"], [45])
+    context = runner.build_context([StepEntry("a", tokens, [44])])
     context.layer_trace = []
     runner.model.forward(context, runner.layer_caches)
     assert len(context.layer_trace) == len(want)

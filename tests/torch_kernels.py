@@ -266,7 +266,14 @@ def gated_rmsnorm(x, gate, weight, eps, out, heads):
     return out
 
 
-def short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation="silu"):
+def short_conv_step(x, taps, tail, seq_of_token, query_start_loc, state_slots, num_seqs, out, activation="silu",
+                    single_tokens=False):
+    short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation)
+    short_conv_update(x, tail, query_start_loc, state_slots, num_seqs)
+    return out
+
+
+def short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation="silu", move_tail=False):
     K = taps.shape[1]
     qsl, slots = query_start_loc.tolist(), state_slots.tolist()
     out.zero_()
@@ -293,7 +300,8 @@ def short_conv_update(x, tail, query_start_loc, state_slots, num_seqs):
 
 
 def gated_delta_rule(qkv, ab, a_log, dt_bias, state, query_start_loc, state_slots, num_seqs, heads, kv_heads, dim,
-                     vdim, out):
+                     vdim, out, max_query_len=0):
+    """state: [slots, heads, vdim, dim], the transpose of S [dim, vdim] per head."""
     qsl, slots = query_start_loc.tolist(), state_slots.tolist()
     T = qkv.shape[0]
     qk = kv_heads * dim
@@ -306,7 +314,7 @@ def gated_delta_rule(qkv, ab, a_log, dt_bias, state, query_start_loc, state_slot
     decay = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(ab[:, heads:].float() + dt_bias))
     for s in range(num_seqs):
         for t in range(qsl[s], qsl[s + 1]):
-            S = state[slots[s]]
+            S = state[slots[s]].transpose(1, 2)       # a view: [heads, dim, vdim]
             for h in range(heads):
                 g = h // (heads // kv_heads)
                 S[h] *= decay[t, h]
@@ -373,5 +381,5 @@ def fused_decode_supports(*args) -> bool:
 
 
 ALL = ("convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
-       "short_conv", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
+       "short_conv", "short_conv_step", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
