@@ -315,8 +315,9 @@ def _kegizen_config(width: int, ff: int, layers: int, heads: int, kv_heads: int,
             "layers": [attention if i % 4 == 3 else delta for i in range(layers)], "loop": None}
 
 
-def _timed(fn, repeats: int = 20, warmup: int = 5) -> float:
-    """Median milliseconds of `fn()` on the current stream, between CUDA events, after `warmup` calls."""
+def _timed(fn, repeats: int = 20, warmup: int = 5, inner: int = 1) -> float:
+    """Median milliseconds of one `fn()` on the current stream, between CUDA events, after `warmup` calls; with
+    `inner` > 1 that many calls stand between the events (a kernel shorter than the host's time to launch it)."""
     import torch
 
     for _ in range(warmup):
@@ -324,11 +325,13 @@ def _timed(fn, repeats: int = 20, warmup: int = 5) -> float:
     times = []
     for _ in range(repeats):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
         a.record()
-        fn()
+        for _ in range(inner):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        times.append(a.elapsed_time(b) / inner)
     return statistics.median(times)
 
 
@@ -348,6 +351,17 @@ def _kegizen_kernels(peaks: dict) -> dict:
     def ints(v):
         return torch.tensor(v, dtype=torch.int32, device=dev)
 
+    def in_graph(fn, inner: int = 10) -> float:
+        """Milliseconds of one `fn()` replayed from a CUDA graph of `inner` calls (kernels of a few microseconds,
+        which the host cannot launch as fast as they run)."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, repeats=10, warmup=2) / inner
+
     # -- norms over a stream of 16,384 x 2,048 (the 32-bit stream: 134 MB; bfloat16: 67 MB)
     T, W = 16384, 2048
     x32, x16 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf)
@@ -360,7 +374,7 @@ def _kegizen_kernels(peaks: dict) -> dict:
 
     # -- short convolutions over 16,384 tokens x 6,144 channels
     C = 6144
-    xin, taps = torch.randn(T, C, device=dev).to(bf), torch.randn(C, 4, device=dev).to(bf)
+    xin, taps = torch.randn(T, C, device=dev).to(bf), torch.randn(4, C, device=dev).to(bf)
     tail, conved = torch.zeros(4, 3, C, dtype=bf, device=dev), torch.empty(T, C, dtype=bf, device=dev)
     seq_of, qsl, slots = torch.zeros(T, dtype=torch.int32, device=dev), ints([0, T]), ints([0])
     ms = _timed(lambda: ops.short_conv(xin, taps, tail, seq_of, qsl, slots, conved))
@@ -377,7 +391,8 @@ def _kegizen_kernels(peaks: dict) -> dict:
         a_log, dt = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
         q2 = ints([i * tokens_each for i in range(batch + 1)])
         sl = ints(list(range(batch)))
-        ms = _timed(lambda: ops.gated_delta_rule(qkv, ab, a_log, dt, state, q2, sl, batch, H, H, d, d, read, tokens_each))
+        run = lambda: ops.gated_delta_rule(qkv, ab, a_log, dt, state, q2, sl, batch, H, H, d, d, read, tokens_each)  # noqa: E731
+        ms = in_graph(run) if tokens_each == 1 else _timed(run)
         out[key + "_us"] = ms * 1e3
         if tokens_each == 1:
             out[key + "_hbm_frac"] = batch * H * d * d * 4 * 2 / (ms * 1e-3) / hbm
@@ -410,9 +425,9 @@ def _kegizen_kernels(peaks: dict) -> dict:
         plan = AttentionPlan(num_decode=B, decode_seqs=ints(list(range(B))), decode_tokens=ints(list(range(B))),
                              max_decode_context_len=n)
         args = (q, q.shape[1], o, k_pool, v_pool, table, ints(list(range(B + 1))), ints([n] * B), B, 1, heads, kv_heads, head_dim, head_dim ** -0.5)
-        ms = _timed(lambda: ops.paged_attention(*args, 1024, plan=plan, keep_first=4, softcap=30.0))
+        ms = in_graph(lambda: ops.paged_attention(*args, 1024, plan=plan, keep_first=4, softcap=30.0))
         out[f"attention_decode_d{head_dim}_masked_hbm_frac"] = B * 1028 * kv_heads * head_dim * 2 * 2 / (ms * 1e-3) / hbm
-        ms = _timed(lambda: ops.paged_attention(*args, 1024, plan=plan))
+        ms = in_graph(lambda: ops.paged_attention(*args, 1024, plan=plan))
         out[f"llama_attention_decode_d{head_dim}_window_hbm_frac"] = B * 1024 * kv_heads * head_dim * 2 * 2 / (ms * 1e-3) / hbm
     return {k: round(v, 4) for k, v in out.items()}
 

@@ -75,7 +75,18 @@ struct TcAttnParams {
   float scale_log2;
   int window;
   int* error_flag;
+  // With a window, the first keep_first keys of a sequence stay visible behind it.  cap_out > 0: an unscaled score
+  // s becomes cap_out * tanh(s * cap_in) and is then scaled like any other (cap_in = scale / cap, cap_out = cap / scale).
+  int keep_first;
+  float cap_in, cap_out;
 };
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)) from one exponential and one division; exact at both ends, a few 1e-7 between.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390082f));
+  return 1.f - __fdividef(2.f, 1.f + e);
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -121,7 +132,9 @@ struct KvStages { static constexpr int value = D == 64 ? 5 : (X == 1 ? 6 : 5); }
 
 template <int X> constexpr int attn_threads() { return 32 + 32 * X + 128 * X; }   // loader, X issuers, X x 4 softmax warps
 
-template <int D, int X>
+// kOptions: kept first keys and the soft-cap are compiled in (a kernel of its own, so that the plain one keeps
+// its registers).
+template <int D, int X, bool kOptions>
 __global__ void __launch_bounds__(attn_threads<X>(), (D == 64 && X == 1) ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const TcAttnParams p) {
@@ -170,7 +183,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto p_full = [&](int b) { return tile_bar(x, 1, b); };
   auto pv_done = [&](int b) { return tile_bar(x, 2, b); };
   const int tile_lo = lo / kKeys, tile_hi = (hi + kKeys - 1) / kKeys;
-  const int ntiles = tile_hi - tile_lo;
+  // The first keys that stay visible behind the window, [0, kept_end): the tiles that hold them and lie before the
+  // window's first tile are walked first (steps 0 .. kept_tiles - 1), then the window's tiles.
+  const int kept_end = (kOptions && p.window > 0 && p.keep_first > 0) ? min(p.keep_first, lo) : 0;
+  const int kept_tiles = min((kept_end + kKeys - 1) / kKeys, tile_lo);
+  const int ntiles = kept_tiles + tile_hi - tile_lo;
+  auto tile_at = [&](int t) { return t < kept_tiles ? t : tile_lo + t - kept_tiles; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kKvStages; ++s) {
@@ -205,8 +223,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto load_tile = [&](int t, bool stage_is_new) -> bool {
     const int stage = t % kKvStages;
     const unsigned phase = (unsigned)(t / kKvStages) & 1;
-    const int kpos = (tile_lo + t) * kKeys + lane * p.page_size;
-    const int first_page = ((tile_lo + t) * kKeys) >> p.page_shift;
+    const int kpos = tile_at(t) * kKeys + lane * p.page_size;
+    const int first_page = (tile_at(t) * kKeys) >> p.page_shift;
     if ((first_page >> 5) != chunk) {
       entries = (first_page >> 5) == chunk + 1 && chunk >= 0 ? entries_ahead : table_chunk(first_page >> 5);
       chunk = first_page >> 5;
@@ -214,7 +232,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     }
     const int page = __shfl_sync(0xffffffffu, entries, (first_page + lane) & 31);
     int row = -1;
-    if (lane < boxes && kpos < hi && kpos + p.page_size > lo && page >= 0 && page < p.num_pages)
+    if (lane < boxes && kpos < hi && (kpos + p.page_size > lo || kpos < kept_end) && page >= 0 && page < p.num_pages)
       row = (page * p.kv_heads + kvh) * p.page_size;
     const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
     bool fine = true;
@@ -334,7 +352,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     bool ok = true;
     for (int t = 0; ok && t < ntiles; ++t) {
       const int buf = t & 1, stage = t % kKvStages;
-      const int key0 = (tile_lo + t) * kKeys;
+      const int key0 = tile_at(t) * kKeys;
       if (!mbar_wait(s_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 16)) { ok = false; break; }
       tcgen05_fence_after();
       unsigned sa[32], sb[32];
@@ -343,6 +361,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tmem_load32(tmem_s[buf] + lane_field + 32, sb);
       tmem_load_wait();
 
+      if (kOptions && p.cap_out > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sa[j] = __float_as_uint(p.cap_out * tanh_fast(__uint_as_float(sa[j]) * p.cap_in));
+          sb[j] = __float_as_uint(p.cap_out * tanh_fast(__uint_as_float(sb[j]) * p.cap_in));
+        }
+      }
       const bool all_visible = key0 + kKeys - 1 <= first_qpos && (p.window <= 0 || key0 > last_qpos - p.window);
       float mx = m;
       if (all_visible && qpos >= 0) {
@@ -354,8 +379,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int ka = key0 + j, kb = key0 + 32 + j;
-          const bool va = ka <= qpos && (p.window <= 0 || ka > qpos - p.window);
-          const bool vb = kb <= qpos && (p.window <= 0 || kb > qpos - p.window);
+          const bool va = ka <= qpos && (p.window <= 0 || ka > qpos - p.window || (kOptions && ka < p.keep_first));
+          const bool vb = kb <= qpos && (p.window <= 0 || kb > qpos - p.window || (kOptions && kb < p.keep_first));
           if (!va) sa[j] = __float_as_uint(-INFINITY);
           if (!vb) sb[j] = __float_as_uint(-INFINITY);
           mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
@@ -414,7 +439,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         for (int e = threadIdx.x - 32 * (1 + X) - 128 * x; e < kSub * kKeys * 8; e += 128) {
           const int sub = e / (kKeys * 8), key = (e >> 3) % kKeys;
           const int kpos = key0 + key;
-          if (kpos < lo || kpos >= hi)
+          if ((kpos < lo && kpos >= kept_end) || kpos >= hi)
             *reinterpret_cast<uint4*>(vt + sub * kKeySubBytes + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
         fence_async_shared();
@@ -487,20 +512,31 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int pag
   return true;
 }
 
+template <int D, int X, bool kOptions>
+static int launch_tc_attention_as(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
+                                  cudaStream_t stream);
+
 template <int D, int X>
 static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
                                cudaStream_t stream) {
+  return (p.keep_first > 0 || p.cap_out > 0.f) ? launch_tc_attention_as<D, X, true>(mk, mv, p, grid, stream)
+                                                : launch_tc_attention_as<D, X, false>(mk, mv, p, grid, stream);
+}
+
+template <int D, int X, bool kOptions>
+static int launch_tc_attention_as(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
+                                  cudaStream_t stream) {
   constexpr int kKvStages = KvStages<D, X>::value;
   constexpr size_t smem = (size_t)X * (D / 64) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
                           8 * (3 * kKvStages + 6 * X + 2) + 16 + 1024;
   static_assert(smem <= 232448, "more shared memory than a block may have");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D, X, kOptions>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(0, attention_tcgen05_kernel<D, X>, grid, dim3(attn_threads<X>()), smem, stream, mk, mv, p);
+  return (int)launch_pdl(0, attention_tcgen05_kernel<D, X, kOptions>, grid, dim3(attn_threads<X>()), smem, stream, mk, mv, p);
 }
 
 }  // namespace li
@@ -522,8 +558,9 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                                          int table_stride, const int* query_start_loc, const int* context_lens,
                                          const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
                                          int head_dim, int page_size, int num_pages, float scale, int window,
-                                         int* error_flag, cudaStream_t stream) {
+                                         int* error_flag, int keep_first, float softcap, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (softcap > 0.f && scale == 0.f) return LI_ERR_UNSUPPORTED;
   if (!li_paged_attention_tcgen05_supports(heads, kv_heads, head_dim, page_size)) return LI_ERR_UNSUPPORTED;
   if (num_seqs > 65535 || (max_q_len + 0L) * heads / kv_heads / kRows >= 65535) return LI_ERR_UNSUPPORTED;
   if ((q_row_stride % 8) || (out_row_stride % 8) || !aligned16(q) || !aligned16(out) || !aligned16(k_pool) ||
@@ -537,7 +574,8 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
   while ((1 << shift) < page_size) ++shift;
   TcAttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, block_table, table_stride,
                  query_start_loc, context_lens, seq_index, heads, kv_heads, page_size, shift, num_pages,
-                 scale * kLog2eF, window, error_flag};
+                 scale * kLog2eF, window, error_flag, window > 0 && keep_first > 0 ? keep_first : 0,
+                 softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
   // Two query tiles per block at head size 128 where some sequence brings enough queries for two

@@ -1,7 +1,8 @@
 // The gated delta rule and the short convolutions in front of it.
 //
-//   li_short_conv         y[t, c] = act(sum_m w[c, m] * x[t - (K-1-m), c]): a causal convolution over time per
-//                         channel; inputs before the step come from the request's tail (its last K-1 inputs)
+//   li_short_conv         y[t, c] = act(sum_m w[m, c] * x[t - (K-1-m), c]): a causal convolution over time per
+//                         channel (the taps tap by tap, [K, channels], so that neighbouring channels' weights are
+//                         neighbours); inputs before the step come from the request's tail (its last K-1 inputs)
 //   li_short_conv_update  moves every request's tail on by the step's inputs
 //   li_gated_delta_rule   per request and head a state S [dim, vdim] in 32-bit (kept column by column); per token
 //                             S *= g;  u = beta * (v - S^T k);  S += k u^T;  o = S^T q
@@ -43,7 +44,7 @@ __global__ void short_conv_kernel(const T* __restrict__ x, size_t x_stride, cons
     const int back = K - 1 - m;
     const float in = back <= j ? to_float(x[(size_t)(t - back) * x_stride + c])
                                : to_float(old[(size_t)(K - 1 + j - back) * channels + c]);
-    acc = fmaf(to_float(taps[(size_t)c * K + m]), in, acc);
+    acc = fmaf(to_float(taps[(size_t)m * channels + c]), in, acc);
   }
   if (act) acc = acc / (1.0f + expf(-acc));
   out[(size_t)t * channels + c] = from_float<T>(acc);
@@ -81,8 +82,9 @@ __global__ void short_conv_vec_kernel(const T* __restrict__ x, size_t x_stride, 
     const int back = K - 1 - m;
     const Vec16<T> in = back <= j ? load16(x + (size_t)(t - back) * x_stride + c)
                                   : load16(old + (size_t)(K - 1 + j - back) * channels + c);
+    const Vec16<T> w = load16(taps + (size_t)m * channels + c);
 #pragma unroll
-    for (int e = 0; e < N; ++e) acc[e] = fmaf(to_float(taps[(size_t)(c + e) * K + m]), in.get(e), acc[e]);
+    for (int e = 0; e < N; ++e) acc[e] = fmaf(w.get(e), in.get(e), acc[e]);
     // A step of one token (j = 0): tap m read tail entry m (or the token itself, m = K - 1), which becomes entry m - 1.
     if (move_tail != nullptr && m >= 1)
       store16(move_tail + ((size_t)state_slots[seq] * (K - 1) + (m - 1)) * channels + c, in);
@@ -348,7 +350,8 @@ LI_EXPORT int li_short_conv(int dtype, const void* x, size_t x_stride, const voi
   // move_tail: every sequence of the step brings exactly one token and the caller wants the tail moved on by
   // this launch; only the vector kernel does that (LI_ERR_UNSUPPORTED otherwise: the caller then updates apart).
   const int lanes = dtype == kFloat32 ? 4 : 8;     // channels in a 16-byte vector
-  if (channels % lanes == 0 && x_stride % lanes == 0 && aligned16(x) && aligned16(out) && (K == 1 || aligned16(tail))) {
+  if (channels % lanes == 0 && x_stride % lanes == 0 && aligned16(x) && aligned16(out) && aligned16(taps) &&
+      (K == 1 || aligned16(tail))) {
     const int vectors = channels / lanes;
     const dim3 vgrid(tokens, (vectors + 127) / 128);
     if (dtype == kFloat32)

@@ -75,7 +75,7 @@ _SIGNATURES = {
     "li_paged_attention_mma_decode_capacity": ("attention_mma", [c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_float, c_void_p]),
     "li_paged_attention_tcgen05_supports": ("attention_tcgen05", [c_int, c_int, c_int, c_int]),
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
@@ -766,17 +766,19 @@ def fused_decode_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_di
 
 
 def paged_attention_tcgen05(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
-                            seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0) -> torch.Tensor:
-    """The tcgen05 / TMA / tensor-memory attention kernel for prompts and portions (bfloat16, head size 64,
-    pages of 16, 32 or 64 tokens, groups of at most 128 heads).  `gemm_error_flag(device)` tells afterwards whether a
-    wait inside the kernel ever gave up."""
+                            seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, keep_first=0,
+                            softcap=0.0) -> torch.Tensor:
+    """The tcgen05 / TMA / tensor-memory attention kernel for prompts and portions (bfloat16, head size 64 or 128,
+    pages of 16, 32 or 64 tokens, groups of at most 128 heads; `keep_first` and `softcap` as in `paged_attention`).
+    `gemm_error_flag(device)` tells afterwards whether a wait inside the kernel ever gave up."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape
     _check(_fn("li_paged_attention_tcgen05")(
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), scratch_for(q.device).gemm_error.data_ptr(), _stream()), "paged_attention_tcgen05")
+        int(window), scratch_for(q.device).gemm_error.data_ptr(), int(keep_first), float(softcap), _stream()),
+        "paged_attention_tcgen05")
     return out
 
 
@@ -794,6 +796,10 @@ def stream_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, hea
 
 def mma_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and heads // kv_heads <= 64
+
+
+# LITEINFER_TCGEN05_ATTN=0: prompts and portions run on the mma.sync kernel (a switch for measurements).
+MASKED_ON_MMA = os.environ.get("LITEINFER_TCGEN05_ATTN", "1") == "0"
 
 
 def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
@@ -828,15 +834,16 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                                        context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
                                        keep_first, softcap)
     common = (q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
-    # Kept first keys and capped scores are options of the mma.sync kernel only (prompts and single tokens alike).
+    # Kept first keys and capped scores are options of the tcgen05 kernel (prompts) and of the mma.sync kernel
+    # (prompts it takes instead, and single tokens); the streaming decode kernel knows neither.
     options = dict(keep_first=keep_first, softcap=softcap) if masked else {}
     if plan is None:
         return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
                                    **options)
     if plan.num_prefill:
-        if not masked and tcgen05_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size):
+        if tcgen05_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size) and not MASKED_ON_MMA:
             paged_attention_tcgen05(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
-                                    kv_heads, head_dim, scale, window)
+                                    kv_heads, head_dim, scale, window, **options)
         else:
             paged_attention_mma(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
                                 kv_heads, head_dim, scale, window, **options)
@@ -973,7 +980,7 @@ def short_conv(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_t
     """A short causal convolution over time per channel, then the activation.
 
     x [tokens, channels] (a column slice is fine): this step's inputs, every sequence's end to end.  taps
-    [channels, K]: column K-1 multiplies the current token, K-2 the one before.  tail [slots, K-1, channels]: the
+    [K, channels] (tap by tap): row K-1 multiplies the current token, K-2 the one before.  tail [slots, K-1, channels]: the
     last K-1 inputs of each request before this step (zeros at its start), oldest first; it is read, not written
     (`short_conv_update` moves it on).  Tokens whose sequence is -1 give zeros.  `move_tail` (only for steps in
     which every sequence brings exactly one token): the launch also moves the tails on; None is returned, and
@@ -982,8 +989,8 @@ def short_conv(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, seq_of_t
     _on_gpu(taps, tail, seq_of_token, query_start_loc, state_slots, out)
     _int32(seq_of_token, "seq_of_token"); _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
     tokens, channels = x.shape
-    K = taps.shape[1]
-    assert taps.shape[0] == channels and out.shape == (tokens, channels) and out.dtype == x.dtype == taps.dtype
+    K = taps.shape[0]
+    assert taps.shape[1] == channels and out.shape == (tokens, channels) and out.dtype == x.dtype == taps.dtype
     assert tail.shape[1:] == (K - 1, channels) and tail.dtype == x.dtype
     if activation not in ("silu", "none"):
         raise KernelLibraryError(f"short_conv knows the activations 'silu' and 'none', not {activation!r}")

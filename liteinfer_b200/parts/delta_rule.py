@@ -67,7 +67,8 @@ class GatedDeltaRule:
         if pad:
             parts.append(torch.zeros((pad, self.hidden_size), dtype=parts[0].dtype, device=parts[0].device))
         self.in_weight = torch.cat(parts).contiguous()
-        self.conv_weight = torch.cat([tensors[n + "_conv.weight"] for n in ("q", "k", "v")]).contiguous()
+        # The taps of q, k and v's channels side by side, tap by tap: [taps, channels].
+        self.conv_weight = torch.cat([tensors[n + "_conv.weight"] for n in ("q", "k", "v")]).t().contiguous()
         self.a_log, self.dt_bias = tensors["A_log"].contiguous(), tensors["dt_bias"].contiguous()
         self.norm_weight, self.o_weight = tensors["norm.weight"].contiguous(), tensors["o_proj.weight"]
 

@@ -131,7 +131,7 @@ def test_short_conv_in_portions_equals_whole(dtype, taps):
 
     channels, lengths, slots = (72 if taps != 2 else 70), (23, 9), _ints([5, 2])       # 72: the vector kernels' sizes
     x = [_randn(n, channels + 8, seed=10 + i, dtype=dtype) for i, n in enumerate(lengths)]
-    w = _randn(channels, taps, seed=3, scale=0.5, dtype=dtype)
+    w = _randn(taps, channels, seed=3, scale=0.5, dtype=dtype)
 
     def run(impl, cuts):
         tail = torch.zeros(8, taps - 1, channels, dtype=dtype, device=DEV)
@@ -164,7 +164,7 @@ def test_short_conv_in_portions_equals_whole(dtype, taps):
 def test_short_conv_skips_padding():
     from liteinfer_b200 import ops
 
-    x, w = _randn(6, 16, seed=1), _randn(16, 3, seed=2)
+    x, w = _randn(6, 16, seed=1), _randn(3, 16, seed=2)
     tail = _randn(4, 2, 16, seed=3)
     before = tail.clone()
     out = torch.full((6, 16), 7.0, device=DEV)
@@ -322,20 +322,26 @@ def test_tensor_core_attention_with_kept_tokens_and_softcap(head_dim, window, ke
         torch.testing.assert_close(out.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
 
 
-@pytest.mark.parametrize("decode", [False, True])
-def test_tensor_core_attention_edges_stand_out(decode):
-    """As `test_attention_edges_of_window_and_kept_tokens_stand_out`, on the mma.sync kernel (bfloat16, head 64),
-    with edges inside a key tile and on a tile's border."""
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05", "decode"])
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_tensor_core_attention_edges_stand_out(kernel, head_dim):
+    """As `test_attention_edges_of_window_and_kept_tokens_stand_out`, on the tensor-core kernels (bfloat16): the
+    mma.sync kernel on a prompt and on a split single token, the tcgen05 kernel on a prompt; edges inside a key
+    tile and on a tile's border."""
     from liteinfer_b200 import ops
     from liteinfer_b200.parts.context import AttentionPlan
 
-    head_dim, page, n, dtype = 64, 16, 400, torch.bfloat16
+    page, n, dtype = 16, 400, torch.bfloat16
+    decode = kernel == "decode"
     for window, keep in ((143, 5), (128, 64), (208, 70)):
         case = _paged_case((n,), (1 if decode else n,), 1, head_dim, head_dim, page, dtype, seed=4)
         case.k_pool.mul_(0.01)
         pos = n - 1
-        plan = (AttentionPlan(num_decode=1, decode_seqs=_ints([0]), decode_tokens=_ints([0]), max_decode_context_len=n)
-                if decode else None)
+        plan = None
+        if decode:
+            plan = AttentionPlan(num_decode=1, decode_seqs=_ints([0]), decode_tokens=_ints([0]), max_decode_context_len=n)
+        elif kernel == "tcgen05":
+            plan = AttentionPlan(num_prefill=1, prefill_seqs=_ints([0]), max_prefill_query_len=n)
         for key, seen in ((pos - window + 1, True), (pos - window, False), (keep - 1, True), (keep, False), (0, True)):
             k_pool = case.k_pool.clone()
             slot = int(case.table[0, key // page])

@@ -274,7 +274,7 @@ def short_conv_step(x, taps, tail, seq_of_token, query_start_loc, state_slots, n
 
 
 def short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, activation="silu", move_tail=False):
-    K = taps.shape[1]
+    K = taps.shape[0]                  # taps: [K, channels]
     qsl, slots = query_start_loc.tolist(), state_slots.tolist()
     out.zero_()
     for s in range(len(qsl) - 1):
@@ -284,7 +284,7 @@ def short_conv(x, taps, tail, seq_of_token, query_start_loc, state_slots, out, a
         padded = torch.cat([tail[slots[s]].float(), x[a:b].float()])
         acc = torch.zeros(b - a, x.shape[1], device=x.device)
         for j in range(K):
-            acc = acc + padded[j:j + b - a] * taps[:, j].float()
+            acc = acc + padded[j:j + b - a] * taps[j].float()
         out[a:b] = (acc / (1.0 + torch.exp(-acc)) if activation == "silu" else acc).to(out.dtype)
     return out
 
