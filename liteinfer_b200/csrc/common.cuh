@@ -93,6 +93,23 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<
   *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
 }
 
+// The floats of a 16-byte vector.  bfloat16 is widened with shifts and masks: the conversion instruction runs on
+// the conversion pipe at a sixteenth of the rate of the integer one, which a kernel that widens a few dozen
+// values per thread and step feels (measured on the recurrence kernel of delta_rule.cu: that pipe was 65 % busy).
+__device__ __forceinline__ void unpack16(const Vec16<float>& v, float* dst) {
+  dst[0] = v.raw.x; dst[1] = v.raw.y; dst[2] = v.raw.z; dst[3] = v.raw.w;
+}
+__device__ __forceinline__ void unpack16(const Vec16<bf16>& v, float* dst) {
+  const unsigned w[4] = {v.raw.x, v.raw.y, v.raw.z, v.raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    dst[2 * i] = __uint_as_float(w[i] << 16);
+    dst[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ float widen(float x) { return x; }
+__device__ __forceinline__ float widen(bf16 x) { return __uint_as_float((unsigned)__bfloat16_as_ushort(x) << 16); }
+
 // ---- rotary pairs ---------------------------------------------------------------------------------
 // (a, b) = dimensions (j, j + half) of a head, rotated by the angle whose cosine and sine are c and s.  Every
 // product and sum is rounded on its own, whichever kernel the rotation is part of, so that all of them agree

@@ -82,15 +82,21 @@ __global__ void short_conv_vec_kernel(const T* __restrict__ x, size_t x_stride, 
     const int back = K - 1 - m;
     const Vec16<T> in = back <= j ? load16(x + (size_t)(t - back) * x_stride + c)
                                   : load16(old + (size_t)(K - 1 + j - back) * channels + c);
-    const Vec16<T> w = load16(taps + (size_t)m * channels + c);
+    float w[N], v[N];
+    unpack16(load16(taps + (size_t)m * channels + c), w);
+    unpack16(in, v);
 #pragma unroll
-    for (int e = 0; e < N; ++e) acc[e] = fmaf(w.get(e), in.get(e), acc[e]);
+    for (int e = 0; e < N; ++e) acc[e] = fmaf(w[e], v[e], acc[e]);
     // A step of one token (j = 0): tap m read tail entry m (or the token itself, m = K - 1), which becomes entry m - 1.
     if (move_tail != nullptr && m >= 1)
       store16(move_tail + ((size_t)state_slots[seq] * (K - 1) + (m - 1)) * channels + c, in);
   }
 #pragma unroll
-  for (int e = 0; e < N; ++e) result.set(e, act ? acc[e] / (1.0f + expf(-acc[e])) : acc[e]);
+  for (int e = 0; e < N; ++e) {
+    // bfloat16 results take the fast exponential and division (relative error about 1e-6, far inside the rounding).
+    const float sig = sizeof(T) == 2 ? __fdividef(1.0f, 1.0f + __expf(-acc[e])) : 1.0f / (1.0f + expf(-acc[e]));
+    result.set(e, act ? acc[e] * sig : acc[e]);
+  }
   store16(out + (size_t)t * channels + c, result);
 }
 
@@ -122,9 +128,9 @@ __device__ __forceinline__ float sum_over_column_lanes(float v) {   // the eight
 }
 
 // What of a token does not depend on the state, once per (token, head) instead of once per column of S:
-// scales [tokens][kv_heads][2] = (dim^-0.5 / |q|, 1 / |k|) with |x| = sqrt(sum x^2 + 1e-6), and gates
-// [tokens][heads][2] = (beta, g) = (sigmoid(raw_b), exp(-exp(A_log) * softplus(raw_a + dt_bias))).  One warp a
-// (token, head or kv head).
+// units [tokens][kv_heads][2][dim] = (q dim^-0.5 / |q|, k / |k|) in float with |x| = sqrt(sum x^2 + 1e-6), and
+// gates [tokens][heads][2] = (beta, g) = (sigmoid(raw_b), exp(-exp(A_log) * softplus(raw_a + dt_bias))).  One warp
+// a (token, head or kv head).
 template <typename T>
 __global__ void delta_gates_kernel(const T* __restrict__ qkv, size_t row_width, const T* __restrict__ ab,
                                    size_t ab_stride, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -148,9 +154,11 @@ __global__ void delta_gates_kernel(const T* __restrict__ qkv, size_t row_width, 
     }
     qq = warp_sum(qq);
     kk = warp_sum(kk);
-    if (lane == 0) {
-      scales[(t * kv_heads + what) * 2] = (1.0f / sqrtf((float)dim)) / sqrtf(qq + 1e-6f);
-      scales[(t * kv_heads + what) * 2 + 1] = 1.0f / sqrtf(kk + 1e-6f);
+    const float q_inv = (1.0f / sqrtf((float)dim)) / sqrtf(qq + 1e-6f), k_inv = 1.0f / sqrtf(kk + 1e-6f);
+    float* unit = scales + (t * kv_heads + what) * 2 * (size_t)dim;
+    for (int i = lane; i < dim; i += 32) {
+      unit[i] = to_float(q[i]) * q_inv;
+      unit[dim + i] = to_float(k[i]) * k_inv;
     }
   } else {
     const int head = (what - kv_heads) * 32 + lane;
@@ -169,11 +177,7 @@ __device__ __forceinline__ void load_slice(float (&dst)[R], const T* __restrict_
   if (kVector) {
     constexpr int N = Vec16<T>::N;
 #pragma unroll
-    for (int c = 0; c < R / N; ++c) {
-      const Vec16<T> v = load16(p + c * N);
-#pragma unroll
-      for (int e = 0; e < N; ++e) dst[c * N + e] = v.get(e);
-    }
+    for (int c = 0; c < R / N; ++c) unpack16(load16(p + c * N), dst + c * N);
   } else {
 #pragma unroll
     for (int r = 0; r < R; ++r) dst[r] = r < live ? to_float(p[r]) : 0.f;
@@ -228,9 +232,18 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
   DeltaToken<R> ring[kAhead];
   auto fetch = [&](DeltaToken<R>& tok, int t) {
     const T* row = qkv + (size_t)t * row_width;
+    tok.v = widen(row[v_at]);
+    if (kAhead > 1) {
+      // From the kernel in front: q and k as unit vectors in float, and the gates.
+      const float* unit = scales + ((size_t)t * kv_heads + kv_head) * 2 * (size_t)dim + first;
+      load_slice<float, R, kVector>(tok.q, unit, mine_dims);
+      load_slice<float, R, kVector>(tok.k, unit + dim, mine_dims);
+      const float2 ga = *reinterpret_cast<const float2*>(gates + ((size_t)t * heads + head) * 2);
+      tok.q_inv = 1.f; tok.k_inv = 1.f; tok.beta = ga.x; tok.g = ga.y;
+      return;
+    }
     load_slice<T, R, kVector>(tok.q, row + q_at, mine_dims);
     load_slice<T, R, kVector>(tok.k, row + k_at, mine_dims);
-    tok.v = to_float(row[v_at]);
     if (kAhead == 1) {
       // Steps of single tokens: no kernel in front; the block works out the token's scales and gates itself.
       float qq = 0.f, kk = 0.f;
@@ -248,12 +261,12 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
       const float soft = z > 20.f ? z : log1pf(expf(z));
       tok.beta = 1.0f / (1.0f + expf(-raw_b));
       tok.g = expf(-expf(a_log[head]) * soft);
-    } else {
-      const float2 sc = *reinterpret_cast<const float2*>(scales + ((size_t)t * kv_heads + kv_head) * 2);
-      const float2 ga = *reinterpret_cast<const float2*>(gates + ((size_t)t * heads + head) * 2);
-      tok.q_inv = sc.x; tok.k_inv = sc.y; tok.beta = ga.x; tok.g = ga.y;
     }
   };
+  // A token's read-out o = S^T q is not on the chain from token to token, only its S is: the lanes' parts of o
+  // are added up together with the next token's parts of S^T k, so a token costs one round of shuffles.
+  float o_parts = 0.f, o_scale = 0.f;
+  int o_token = -1;
   auto step = [&](const DeltaToken<R>& tok, int t) {
     // With S' = g S:  (S'^T k)_j = g k_inv sum_i S_ij k_i;  S <- g S + k (k_inv u)^T;  o_j = q_inv sum_i S_ij q_i.
     float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
@@ -262,7 +275,16 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
       d0 = fmaf(S[r], tok.k[r], d0); d1 = fmaf(S[r + 1], tok.k[r + 1], d1);
       d2 = fmaf(S[r + 2], tok.k[r + 2], d2); d3 = fmaf(S[r + 3], tok.k[r + 3], d3);
     }
-    const float dot = sum_over_column_lanes((d0 + d1) + (d2 + d3)) * (tok.g * tok.k_inv);
+    float dsum = (d0 + d1) + (d2 + d3), osum = o_parts;
+#pragma unroll
+    for (int offset = 4; offset <= 16; offset <<= 1) {
+      const float a = __shfl_xor_sync(0xffffffffu, dsum, offset), b = __shfl_xor_sync(0xffffffffu, osum, offset);
+      dsum += a;
+      osum += b;
+    }
+    if (o_token >= 0 && live && part == 0)
+      out[(size_t)o_token * heads * vdim + (size_t)head * vdim + column] = osum * o_scale;
+    const float dot = dsum * (tok.g * tok.k_inv);
     const float c = tok.beta * (tok.v - dot) * tok.k_inv;
     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
@@ -272,10 +294,27 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
       o0 = fmaf(S[r], tok.q[r], o0); o1 = fmaf(S[r + 1], tok.q[r + 1], o1);
       o2 = fmaf(S[r + 2], tok.q[r + 2], o2); o3 = fmaf(S[r + 3], tok.q[r + 3], o3);
     }
-    const float o = sum_over_column_lanes((o0 + o1) + (o2 + o3)) * tok.q_inv;
-    if (live && part == 0) out[(size_t)t * heads * vdim + (size_t)head * vdim + column] = o;
+    o_parts = (o0 + o1) + (o2 + o3);
+    o_scale = tok.q_inv;
+    o_token = t;
   };
 
+  // Far ahead of the ring, the lines of a token's inputs are asked into the cache: warp w does it for the tokens
+  // whose number is w modulo 8, one lane a 128-byte line (the unit vectors, then v, then the gates).
+  constexpr int kFar = 24;
+  auto ask_ahead = [&](int t) {
+    if (kAhead == 1 || t >= end || ((t - begin) & 7) != warp) return;
+    const int unit_lines = (8 * dim + 127) / 128;
+    const char* where = nullptr;
+    if (lane < unit_lines)
+      where = reinterpret_cast<const char*>(scales + ((size_t)t * kv_heads + kv_head) * 2 * (size_t)dim) + lane * 128;
+    else if (lane == unit_lines)
+      where = reinterpret_cast<const char*>(qkv + (size_t)t * row_width + v_at);
+    else if (lane == unit_lines + 1)
+      where = reinterpret_cast<const char*>(gates + ((size_t)t * heads + head) * 2);
+    if (where != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(where));
+  };
+  for (int t = begin; t < begin + kFar; ++t) ask_ahead(t);
 #pragma unroll
   for (int a = 0; a < kAhead; ++a)
     if (begin + a < end) fetch(ring[a], begin + a);
@@ -283,10 +322,15 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
 #pragma unroll
     for (int a = 0; a < kAhead; ++a) {
       if (t + a < end) {
+        ask_ahead(t + a + kFar);
         step(ring[a], t + a);
         if (t + a + kAhead < end) fetch(ring[a], t + a + kAhead);
       }
     }
+  }
+  {
+    const float o = sum_over_column_lanes(o_parts) * o_scale;       // the last token's read-out
+    if (live && part == 0) out[(size_t)o_token * heads * vdim + (size_t)head * vdim + column] = o;
   }
 
   if (!live) return;
@@ -299,6 +343,154 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
     for (int r = 0; r < R; ++r)
       if (r < mine_dims) mine[r] = S[r];
   }
+}
+
+// The same recurrence for prompts and portions, with the tokens' inputs staged in shared memory: the loads of a
+// register ring several tokens deep share a warp's few scoreboards, so a wait for one token's inputs also waits
+// for the ones just asked for, and a token cost a whole trip to the second-level cache (0.5 us, whatever the head
+// size).  Here a block copies eight tokens at a time (unit q and k in float, gates, the block's 32 values of v)
+// with cp.async, whose groups are waited for in order, two chunks in flight, and reads them with shared-memory
+// loads.  For dim == 8 R, vdim a multiple of 32 and 16-byte aligned rows.
+constexpr int kStageTokens = 8;
+
+template <typename T, int R>
+__global__ void __launch_bounds__(128)
+gated_delta_rule_staged_kernel(const T* __restrict__ qkv, const float* __restrict__ units, const float* __restrict__ gates,
+                               float* __restrict__ state, const int* __restrict__ query_start_loc,
+                               const int* __restrict__ state_slots, float* __restrict__ out, int heads, int kv_heads,
+                               int vdim) {
+  // Four warps; a lane keeps its eighth of TWO neighbouring columns, so that a warp has two chains to fill the
+  // waits of each other (shuffles, shared-memory loads) and a scheduler has one warp, which it never has to choose.
+  extern __shared__ __align__(16) unsigned char staged[];
+  constexpr int dim = 8 * R;
+  constexpr int kUnitBytes = 8 * dim, kValueBytes = 32 * (int)sizeof(T);
+  constexpr int kTokenBytes = kUnitBytes + 16 + kValueBytes;           // units | gates (8 bytes, padded) | v
+  constexpr int kCopies = kUnitBytes / 16 + 1 + kValueBytes / 16;      // per token: 16-byte copies, one of 8 for the gates
+  grid_dependency_wait();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int begin = query_start_loc[seq], end = query_start_loc[seq + 1];
+  if (end <= begin) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = lane >> 2;
+  const int local_column = warp * 8 + (lane & 3) * 2, column = blockIdx.x * 32 + local_column;   // and the next one
+  const int first = part * R;
+  const int qk_width = kv_heads * dim;
+  const size_t row_width = 2 * (size_t)qk_width + (size_t)heads * vdim;
+  const int kv_head = head / (heads / kv_heads);
+  const size_t v_at = 2 * (size_t)qk_width + (size_t)head * vdim + (size_t)blockIdx.x * 32;
+  float* mine = state + (((size_t)state_slots[seq] * heads + head) * vdim + column) * dim + first;   // column + 1: + dim
+
+  float S[2][R];
+#pragma unroll
+  for (int x = 0; x < 2; ++x)
+#pragma unroll
+    for (int c = 0; c < R / 4; ++c) {
+      const float4 v = *reinterpret_cast<const float4*>(mine + x * dim + c * 4);
+      S[x][c * 4] = v.x; S[x][c * 4 + 1] = v.y; S[x][c * 4 + 2] = v.z; S[x][c * 4 + 3] = v.w;
+    }
+
+  auto copy_chunk = [&](int chunk) {
+    unsigned char* buffer = staged + (size_t)(chunk & 1) * kStageTokens * kTokenBytes;
+    const int t0 = begin + chunk * kStageTokens;
+    for (int i = threadIdx.x; i < kStageTokens * kCopies; i += 128) {
+      const int j = i / kCopies, c = i - j * kCopies, t = t0 + j;
+      if (t >= end) continue;
+      unsigned char* dst = buffer + (size_t)j * kTokenBytes;
+      if (c < kUnitBytes / 16) {
+        const char* src = reinterpret_cast<const char*>(units + ((size_t)t * kv_heads + kv_head) * 2 * dim) + c * 16;
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst + c * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+      } else if (c == kUnitBytes / 16) {
+        const char* src = reinterpret_cast<const char*>(gates + ((size_t)t * heads + head) * 2);
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst + kUnitBytes);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src));
+      } else {
+        const int k = c - kUnitBytes / 16 - 1;
+        const char* src = reinterpret_cast<const char*>(qkv + (size_t)t * row_width + v_at) + k * 16;
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst + kUnitBytes + 16 + k * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::);
+  };
+
+  float o_parts[2] = {0.f, 0.f};
+  int o_token = -1;
+  const int chunks = (end - begin + kStageTokens - 1) / kStageTokens;
+  copy_chunk(0);
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    if (chunk + 1 < chunks) {
+      copy_chunk(chunk + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const unsigned char* buffer = staged + (size_t)(chunk & 1) * kStageTokens * kTokenBytes;
+    const int t0 = begin + chunk * kStageTokens, count = min(kStageTokens, end - t0);
+#pragma unroll 2
+    for (int j = 0; j < count; ++j) {
+      const unsigned char* tok = buffer + (size_t)j * kTokenBytes;
+      const float* q = reinterpret_cast<const float*>(tok) + first;
+      const float* k = q + dim;
+      const float2 ga = *reinterpret_cast<const float2*>(tok + kUnitBytes);
+      const T* values = reinterpret_cast<const T*>(tok + kUnitBytes + 16) + local_column;
+      const float v[2] = {widen(values[0]), widen(values[1])};
+      float kk[R];
+      float d[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(k + r);
+        kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          d[x][0] = fmaf(S[x][r], k4.x, d[x][0]); d[x][1] = fmaf(S[x][r + 1], k4.y, d[x][1]);
+          d[x][0] = fmaf(S[x][r + 2], k4.z, d[x][0]); d[x][1] = fmaf(S[x][r + 3], k4.w, d[x][1]);
+        }
+      }
+      // The read-outs of the token before are added up over the lanes together with this token's S^T k.
+      float sums[4] = {d[0][0] + d[0][1], d[1][0] + d[1][1], o_parts[0], o_parts[1]};
+#pragma unroll
+      for (int offset = 4; offset <= 16; offset <<= 1) {
+        float other[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, sums[i], offset);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sums[i] += other[i];
+      }
+      if (o_token >= 0 && part == 0)
+        *reinterpret_cast<float2*>(out + (size_t)o_token * heads * vdim + (size_t)head * vdim + column) =
+            make_float2(sums[2], sums[3]);
+      const float c[2] = {ga.x * (v[0] - sums[0] * ga.y), ga.x * (v[1] - sums[1] * ga.y)};
+      float o[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(q + r);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          S[x][r] = fmaf(S[x][r], ga.y, kk[r] * c[x]); S[x][r + 1] = fmaf(S[x][r + 1], ga.y, kk[r + 1] * c[x]);
+          S[x][r + 2] = fmaf(S[x][r + 2], ga.y, kk[r + 2] * c[x]); S[x][r + 3] = fmaf(S[x][r + 3], ga.y, kk[r + 3] * c[x]);
+          o[x][0] = fmaf(S[x][r], q4.x, o[x][0]); o[x][1] = fmaf(S[x][r + 1], q4.y, o[x][1]);
+          o[x][0] = fmaf(S[x][r + 2], q4.z, o[x][0]); o[x][1] = fmaf(S[x][r + 3], q4.w, o[x][1]);
+        }
+      }
+      o_parts[0] = o[0][0] + o[0][1];
+      o_parts[1] = o[1][0] + o[1][1];
+      o_token = t0 + j;
+    }
+    __syncthreads();     // the buffer is written again two chunks on
+  }
+  {
+    const float o0 = sum_over_column_lanes(o_parts[0]), o1 = sum_over_column_lanes(o_parts[1]);
+    if (part == 0)
+      *reinterpret_cast<float2*>(out + (size_t)o_token * heads * vdim + (size_t)head * vdim + column) = make_float2(o0, o1);
+  }
+#pragma unroll
+  for (int x = 0; x < 2; ++x)
+#pragma unroll
+    for (int c = 0; c < R / 4; ++c)
+      *reinterpret_cast<float4*>(mine + x * dim + c * 4) =
+          make_float4(S[x][c * 4], S[x][c * 4 + 1], S[x][c * 4 + 2], S[x][c * 4 + 3]);
 }
 
 template <typename T, int R>
@@ -314,6 +506,11 @@ int launch_delta_r(bool single, bool vector, int tokens, dim3 grid, cudaStream_t
   if (single) {
     if (vector) LI_DELTA(1, true);
     LI_DELTA(1, false);
+  }
+  if (vector && vdim % 32 == 0 && aligned16(scales) && (((size_t)heads * vdim) * sizeof(T)) % 16 == 0) {
+    constexpr size_t smem = 2 * (size_t)kStageTokens * (8 * 8 * R + 16 + 32 * sizeof(T));
+    return (int)launch_pdl(tokens, gated_delta_rule_staged_kernel<T, R>, grid, dim3(128), smem, stream, qkv, scales, gates,
+                           state, qsl, slots, out, heads, kv_heads, vdim);
   }
   if (vector) LI_DELTA(kDeep, true);
   LI_DELTA(kDeep, false);
@@ -386,8 +583,8 @@ LI_EXPORT int li_short_conv_update(int dtype, const void* x, size_t x_stride, vo
 }
 
 // qkv [tokens, 2 * kv_heads * dim + heads * vdim]; ab [tokens, >= 2 * heads] with `ab_stride` elements a row; state
-// [slots, heads, vdim, dim] (column by column); out [tokens, heads * vdim]; scratch: 2 * tokens * (kv_heads + heads)
-// floats.  max_q_len: the most tokens a sequence brings (1 chooses the variant without tokens in flight).
+// [slots, heads, vdim, dim] (column by column); out [tokens, heads * vdim]; scratch: 2 * tokens * (kv_heads * dim +
+// heads) floats.  max_q_len: the most tokens a sequence brings (1 chooses the variant without tokens in flight).
 LI_EXPORT int li_gated_delta_rule(int dtype, const void* qkv, const void* ab, size_t ab_stride, int tokens, int num_seqs,
                                   const float* a_log, const float* dt_bias, float* state, const int* query_start_loc,
                                   const int* state_slots, float* out, int heads, int kv_heads, int dim, int vdim,
@@ -397,7 +594,7 @@ LI_EXPORT int li_gated_delta_rule(int dtype, const void* qkv, const void* ab, si
       num_seqs > 65535 || scratch == nullptr)
     return LI_ERR_UNSUPPORTED;
   float* scales = scratch;
-  float* gates = scratch + 2 * (size_t)tokens * kv_heads;
+  float* gates = scratch + 2 * (size_t)tokens * kv_heads * dim;
   const size_t row_width = 2 * (size_t)kv_heads * dim + (size_t)heads * vdim;
   const size_t items = (size_t)tokens * (kv_heads + (heads + 31) / 32);
   const dim3 gates_grid((unsigned)((items + 7) / 8));

@@ -82,10 +82,9 @@ __device__ __forceinline__ void load4(const float* p, float (&o)[4]) {
   o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
 }
 __device__ __forceinline__ void load4(const bf16* p, float (&o)[4]) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);      // widened with shifts and masks (see unpack16)
+  o[0] = __uint_as_float(raw.x << 16); o[1] = __uint_as_float(raw.x & 0xffff0000u);
+  o[2] = __uint_as_float(raw.y << 16); o[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
 __device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
   *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);

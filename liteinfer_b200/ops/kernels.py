@@ -1041,8 +1041,9 @@ def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, d
     assert a_log.dtype == dt_bias.dtype == state.dtype == out.dtype == torch.float32
     assert a_log.numel() == dt_bias.numel() == heads and state.shape[1:] == (heads, vdim, dim)
     assert out.shape == (tokens, heads * vdim) and heads % kv_heads == 0
-    # What the kernel in front leaves for the recurrence: per token the unit-norm scales and the gates.
-    scratch = torch.empty(2 * max(tokens, 1) * (kv_heads + heads), dtype=torch.float32, device=qkv.device)
+    # What the kernel in front leaves for the recurrence: per token q and k as unit vectors in 32-bit, and the gates.
+    scratch = torch.empty(2 * max(tokens, 1) * (kv_heads * dim + heads) if max_query_len != 1 else 4,
+                          dtype=torch.float32, device=qkv.device)
     _check(_fn("li_gated_delta_rule")(_code(qkv), qkv.data_ptr(), ab.data_ptr(), ab.stride(0), tokens, num_seqs,
                                       a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), query_start_loc.data_ptr(),
                                       state_slots.data_ptr(), out.data_ptr(), heads, kv_heads, dim, vdim,

