@@ -11,6 +11,9 @@ in place by the kernel that stages the batch, and the sampled tokens travel back
 to the host).  `prefill` times one 2,048-token prompt,
 `roofline` relates the decode step to the bytes it must read, `points` holds
 decode at batch 1 and 64.  Weights are random (seeded) and token ids synthetic.
+
+`--compare kegizen` prints another line instead (the default run is unchanged): prefill and decode of the Kegizen
+decoder beside the Llama decoder at equal layer sizes, and the Kegizen kernels one by one beside their like.
 """
 
 from __future__ import annotations

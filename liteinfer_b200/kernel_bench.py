@@ -175,7 +175,27 @@ def rmsnorm(rows: int, width: int) -> dict:
     return {"kernel": "add_rmsnorm", "rows": rows, "width": width, "us": us, "GBps": rows * width * 2 * 4 / us / 1e3}
 
 
+def delta_rule(batch: int, tokens_each: int, heads: int = 16, dim: int = 128, vdim: int = 128) -> dict:
+    """The gated delta rule over `batch` sequences of `tokens_each` tokens (the state starts at zero)."""
+    n = batch * tokens_each
+    qkv = torch.randn(n, 2 * heads * dim + heads * vdim, device="cuda").to(torch.bfloat16)
+    ab = torch.randn(n, 2 * heads, device="cuda").to(torch.bfloat16)
+    state = torch.zeros(batch, heads, vdim, dim, device="cuda")
+    out = torch.empty(n, heads * vdim, device="cuda")
+    a_log, dt_bias = torch.zeros(heads, device="cuda"), torch.zeros(heads, device="cuda")
+    starts = torch.arange(0, n + 1, tokens_each, dtype=torch.int32, device="cuda")
+    slots = torch.arange(batch, dtype=torch.int32, device="cuda")
+    us = _time(lambda i: ops.gated_delta_rule(qkv, ab, a_log, dt_bias, state, starts, slots, batch, heads, heads, dim,
+                                              vdim, out, tokens_each), 2 if tokens_each > 1 else 8)
+    return {"kernel": "gated_delta_rule", "batch": batch, "tokens_each": tokens_each, "us": us,
+            "us_per_token": us / tokens_each, "state_GBps": batch * heads * dim * vdim * 4 * 2 / us / 1e3}
+
+
 CASES = {
+    "delta_rule_prompt_2048": lambda: delta_rule(1, 2048),
+    "delta_rule_prompt_2048_dim64": lambda: delta_rule(1, 2048, heads=32, dim=64, vdim=64),
+    "delta_rule_decode_b8": lambda: delta_rule(8, 1),
+    "delta_rule_decode_b64": lambda: delta_rule(64, 1),
     "decode_attention_b8": lambda: attention(8, 1, 4096),
     "decode_attention_b1": lambda: attention(1, 1, 4096),
     "decode_attention_b64": lambda: attention(64, 1, 4096),

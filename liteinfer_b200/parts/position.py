@@ -84,10 +84,13 @@ class RotaryEmbedding:
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rotary_dim: int | None = None, rope_type: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: float = 0, fast: float = 32.0, slow: float = 1.0) -> None:
+                 original_max_position_embeddings: float = 0, fast: float | None = None,
+                 slow: float | None = None) -> None:
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         scale = 1.0
         if rope_type == "yarn":
+            if fast is None or slow is None or not original_max_position_embeddings > 0:
+                raise ValueError("yarn scaling needs factor, original_max_position_embeddings, fast and slow")
             inv_freq, scale = yarn_inverse_frequencies(self.rotary_dim, theta, factor,
                                                        float(original_max_position_embeddings), fast, slow)
         else:
