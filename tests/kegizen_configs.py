@@ -53,10 +53,34 @@ KEG_C = {
     "loop": {"start": 1, "stop": 2, "times": 1},
 }
 
+# Sizes that the tensor-core attention kernels and the staged recurrence kernel take (keys and values of 64, a state
+# of 64 x 32), with a window, kept tokens, a cap and scaled rotation on them; two passes over both layers.
+KEG_D = {
+    "architecture": "Kegizen", "vocab": 200, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "delta", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 32, "conv": 3}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 12.0,
+                   "mask": {"size": 70, "keep_first": 5},
+                   "rot": {"dims": 64, "base": 5000.0, "scaling": {"factor": 3.0, "original": 64, "fast": 16.0, "slow": 2.0}}}},
+    ],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+
 # name -> (config, seed, page size)
-ALL = {"keg_a": (KEG_A, 11, 16), "keg_b": (KEG_B, 12, 4), "keg_c": (KEG_C, 13, 8)}
+ALL = {"keg_a": (KEG_A, 11, 16), "keg_b": (KEG_B, 12, 4), "keg_c": (KEG_C, 13, 8), "keg_d": (KEG_D, 14, 16)}
 
 
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
     rng = random.Random(seed)
     return [rng.randrange(vocab) for _ in range(length)]
+
+# Largest absolute difference of float32 logits from the float64 plain implementation that rounding alone explains
+# (the plain implementation itself, run in float32, differs from its float64 run by 4e-5 on KEG_D: two passes of
+# layer norms over small sublayer outputs amplify the last bits).
+FLOAT32_TOLERANCE = {"keg_a": 5e-5, "keg_b": 5e-5, "keg_c": 5e-5, "keg_d": 2e-4}
+# The same for bfloat16 (the plain stand-in kernels, run in bfloat16 on a CPU, come to 0.05 and 0.04).  How far
+# rounding carries depends on the sizes: with one q/k head for four value heads in KEG_D's recurrence the same
+# stand-ins differ from float64 by 0.47, every head repeating the same rounded q and k.
+BFLOAT16_TOLERANCE = {"keg_a": 0.06, "keg_b": 0.06, "keg_c": 0.06, "keg_d": 0.1}
