@@ -26,12 +26,22 @@ def expected_logits(model_dir, requests):
     return {name: plain_kegizen.forward(config, tensors, tokens).float() for name, tokens in requests.items()}
 
 
+def one_by_one(trace, requests, tag="o"):
+    """Every token a step of its own, from the first one on (the first tokens of a sequence, and long decoding)."""
+    for name, tokens in requests.items():
+        rid = f"{tag}-{name}"
+        for i, token in enumerate(tokens):
+            trace.add([(rid, [token], [0])], end=[rid] if i == len(tokens) - 1 else [])
+
+
 def full_trace(requests):
     trace = rh.Trace()
     rh.whole(trace, requests)
     rh.tail_decoded(trace, requests, tail=40)
     rh.portions(trace, requests)
     rh.mixed(trace, requests)
+    longest = max(requests, key=lambda name: len(requests[name]))
+    one_by_one(trace, {longest: requests[longest]})
     return trace
 
 
@@ -137,3 +147,36 @@ def test_cache_manager_kept_tokens_and_value_size():
     m.release("a")
     m.check_invariants()
     assert kept.allocator.num_held == 0 and plain.allocator.num_held == 0
+
+
+def test_yarn_frequencies_are_the_plain_ones():
+    from liteinfer_b200.parts.position import yarn_inverse_frequencies
+
+    for dims, base, factor, original, fast, slow in ((16, 10000.0, 4.0, 32, 8.0, 1.0), (12, 1000.0, 8.0, 16, 4.0, 0.5),
+                                                      (64, 5000.0, 3.0, 64, 16.0, 2.0), (8, 100.0, 1.5, 4096, 32.0, 1.0)):
+        got, stretch = yarn_inverse_frequencies(dims, base, factor, float(original), fast, slow)
+        want, want_stretch = plain_kegizen.yarn_frequencies(dims, base, {"factor": factor, "original": original,
+                                                                         "fast": fast, "slow": slow})
+        assert torch.equal(got, want.to(torch.float32)) and stretch == want_stretch
+        plain = base ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / dims)
+        assert bool((want <= plain + 1e-12).all()) and bool((want >= plain / factor - 1e-12).all())
+
+
+def test_layers_one_by_one_against_plain_on_cpu(cpu_kernels, kegizen_dirs):
+    """The residual stream after every stop of the schedule: which layer differs first, if one does."""
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.engine.runner import StepEntry
+
+    for name in ("keg_a", "keg_c"):
+        config, tensors = plain_kegizen.read_model(kegizen_dirs[name])
+        tokens = kc.prompt(config["vocab"], 37, 3)
+        want: list = []
+        plain_kegizen.forward(config, tensors, tokens, want)
+        runner = build_runner(kegizen_dirs[name], torch.float32, "cpu", 8, 8, 2)
+        runner.cache.reserve(["a"], [37])
+        context = runner.build_context([StepEntry("a", tokens, [36])])
+        context.layer_trace = []
+        runner.model.forward(context, runner.layer_caches)
+        assert len(context.layer_trace) == len(want) == len(plain_kegizen.layer_runs(config))
+        for stop, (got, plain) in enumerate(zip(context.layer_trace, want)):
+            assert float((got.double() - plain).abs().max()) < 1e-4, f"{name}: stop {stop}"

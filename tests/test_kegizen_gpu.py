@@ -280,11 +280,14 @@ def test_attention_edges_of_window_and_kept_tokens_stand_out(decode):
     inside and just outside the window, the last kept token and the first one that is not kept."""
     from liteinfer_b200 import ops
 
-    head_dim, v_dim, page, n, window, keep = 16, 24, 8, 90, 21, 5
+    head_dim, v_dim, page, n = 16, 24, 8, 90
     case = _paged_case((n,), (1 if decode else n,), 1, head_dim, v_dim, page, torch.float32, seed=4)
     case.k_pool.mul_(0.01)
     pos = n - 1                                                # the query looked at
-    for key, seen in ((pos - window + 1, True), (pos - window, False), (keep - 1, True), (keep, False), (0, True), (pos, True)):
+    cases = [(21, 5, key, seen) for key, seen in ((pos - 20, True), (pos - 21, False), (4, True), (5, False), (0, True), (pos, True))]
+    cases += [(26, 8, 64, True), (26, 8, 63, False), (26, 8, 7, True), (26, 8, 8, False)]     # both edges on page borders
+    cases += [(0, 0, 0, True), (0, 3, 40, True), (1, 0, pos, True), (1, 0, pos - 1, False)]   # no window: a far key; a window of one
+    for window, keep, key, seen in cases:
         k_pool = case.k_pool.clone()
         slot = int(case.table[0, key // page]) 
         k_pool[slot, 0, key % page] = 0.0
@@ -411,6 +414,9 @@ def test_trace_replay_all_cuts(kegizen_dirs, tmp_path, name, lengths, dtype):
     rh.tail_decoded(trace, requests, tail=40)
     rh.portions(trace, requests)
     rh.mixed(trace, requests)
+    longest = max(requests, key=lambda r: len(requests[r]))
+    for i, token in enumerate(requests[longest]):            # every token a step of its own, from the first one on
+        trace.add([(f"o-{longest}", [token], [0])], end=[f"o-{longest}"] if i == len(requests[longest]) - 1 else [])
     results = rh.run_program(trace, kegizen_dirs[name], dtype, tmp_path / "out", config["vocab"], page_size=page)
     worst, where = rh.worst_error(results, rh.gather_expected(trace, expected))
     limit = 2 * kc.FLOAT32_TOLERANCE[name] if dtype == "float32" else kc.BFLOAT16_TOLERANCE[name]
