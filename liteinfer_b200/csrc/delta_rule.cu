@@ -348,9 +348,9 @@ gated_delta_rule_kernel(const T* __restrict__ qkv, const float* __restrict__ sca
 // The same recurrence for prompts and portions, with the tokens' inputs staged in shared memory: the loads of a
 // register ring several tokens deep share a warp's few scoreboards, so a wait for one token's inputs also waits
 // for the ones just asked for, and a token cost a whole trip to the second-level cache (0.5 us, whatever the head
-// size).  Here a block copies eight tokens at a time (unit q and k in float, gates, the block's 32 values of v)
+// size).  Here a block copies eight tokens at a time (unit q and k in float, gates, the block's 16 values of v)
 // with cp.async, whose groups are waited for in order, two chunks in flight, and reads them with shared-memory
-// loads.  For dim == 8 R, vdim a multiple of 32 and 16-byte aligned rows.
+// loads.  For dim == 8 R, vdim a multiple of 16 and 16-byte aligned rows.
 constexpr int kStageTokens = 8;
 
 template <typename T, int R>
@@ -359,35 +359,34 @@ gated_delta_rule_staged_kernel(const T* __restrict__ qkv, const float* __restric
                                float* __restrict__ state, const int* __restrict__ query_start_loc,
                                const int* __restrict__ state_slots, float* __restrict__ out, int heads, int kv_heads,
                                int vdim) {
-  // Four warps; a lane keeps its eighth of TWO neighbouring columns, so that a warp has two chains to fill the
-  // waits of each other (shuffles, shared-memory loads) and a scheduler has one warp, which it never has to choose.
+  // Four warps and 16 columns a block: a prompt alone is a few hundred chains (heads x vdim columns / 4 a warp),
+  // fewer than the device has schedulers, so each warp gets a scheduler of its own and as little of a column's
+  // arithmetic as the lanes of a column can share.
   extern __shared__ __align__(16) unsigned char staged[];
-  constexpr int dim = 8 * R;
-  constexpr int kUnitBytes = 8 * dim, kValueBytes = 32 * (int)sizeof(T);
-  constexpr int kTokenBytes = kUnitBytes + 16 + kValueBytes;           // units | gates (8 bytes, padded) | v
-  constexpr int kCopies = kUnitBytes / 16 + 1 + kValueBytes / 16;      // per token: 16-byte copies, one of 8 for the gates
+  constexpr int dim = 8 * R, kColumns = 16;
+  constexpr int kUnitBytes = 8 * dim, kValueBytes = kColumns * (int)sizeof(T);
+  constexpr int kTokenBytes = kUnitBytes + 16 + (kValueBytes + 15) / 16 * 16;   // units | gates (8 bytes, padded) | v
+  constexpr int kCopies = kUnitBytes / 16 + 1 + kValueBytes / 16;               // per token: 16-byte copies, one of 8 for the gates
   grid_dependency_wait();
   const int seq = blockIdx.z, head = blockIdx.y;
   const int begin = query_start_loc[seq], end = query_start_loc[seq + 1];
   if (end <= begin) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane >> 2;
-  const int local_column = warp * 8 + (lane & 3) * 2, column = blockIdx.x * 32 + local_column;   // and the next one
+  const int local_column = warp * 4 + (lane & 3), column = blockIdx.x * kColumns + local_column;
   const int first = part * R;
   const int qk_width = kv_heads * dim;
   const size_t row_width = 2 * (size_t)qk_width + (size_t)heads * vdim;
   const int kv_head = head / (heads / kv_heads);
-  const size_t v_at = 2 * (size_t)qk_width + (size_t)head * vdim + (size_t)blockIdx.x * 32;
-  float* mine = state + (((size_t)state_slots[seq] * heads + head) * vdim + column) * dim + first;   // column + 1: + dim
+  const size_t v_at = 2 * (size_t)qk_width + (size_t)head * vdim + (size_t)blockIdx.x * kColumns;
+  float* mine = state + (((size_t)state_slots[seq] * heads + head) * vdim + column) * dim + first;
 
-  float S[2][R];
+  float S[R];
 #pragma unroll
-  for (int x = 0; x < 2; ++x)
-#pragma unroll
-    for (int c = 0; c < R / 4; ++c) {
-      const float4 v = *reinterpret_cast<const float4*>(mine + x * dim + c * 4);
-      S[x][c * 4] = v.x; S[x][c * 4 + 1] = v.y; S[x][c * 4 + 2] = v.z; S[x][c * 4 + 3] = v.w;
-    }
+  for (int c = 0; c < R / 4; ++c) {
+    const float4 v = *reinterpret_cast<const float4*>(mine + c * 4);
+    S[c * 4] = v.x; S[c * 4 + 1] = v.y; S[c * 4 + 2] = v.z; S[c * 4 + 3] = v.w;
+  }
 
   auto copy_chunk = [&](int chunk) {
     unsigned char* buffer = staged + (size_t)(chunk & 1) * kStageTokens * kTokenBytes;
@@ -414,7 +413,7 @@ gated_delta_rule_staged_kernel(const T* __restrict__ qkv, const float* __restric
     asm volatile("cp.async.commit_group;" ::);
   };
 
-  float o_parts[2] = {0.f, 0.f};
+  float o_parts = 0.f;
   int o_token = -1;
   const int chunks = (end - begin + kStageTokens - 1) / kStageTokens;
   copy_chunk(0);
@@ -434,63 +433,47 @@ gated_delta_rule_staged_kernel(const T* __restrict__ qkv, const float* __restric
       const float* q = reinterpret_cast<const float*>(tok) + first;
       const float* k = q + dim;
       const float2 ga = *reinterpret_cast<const float2*>(tok + kUnitBytes);
-      const T* values = reinterpret_cast<const T*>(tok + kUnitBytes + 16) + local_column;
-      const float v[2] = {widen(values[0]), widen(values[1])};
+      const float v = widen(reinterpret_cast<const T*>(tok + kUnitBytes + 16)[local_column]);
       float kk[R];
-      float d[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(k + r);
         kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          d[x][0] = fmaf(S[x][r], k4.x, d[x][0]); d[x][1] = fmaf(S[x][r + 1], k4.y, d[x][1]);
-          d[x][0] = fmaf(S[x][r + 2], k4.z, d[x][0]); d[x][1] = fmaf(S[x][r + 3], k4.w, d[x][1]);
-        }
+        d0 = fmaf(S[r], k4.x, d0); d1 = fmaf(S[r + 1], k4.y, d1);
+        d2 = fmaf(S[r + 2], k4.z, d2); d3 = fmaf(S[r + 3], k4.w, d3);
       }
-      // The read-outs of the token before are added up over the lanes together with this token's S^T k.
-      float sums[4] = {d[0][0] + d[0][1], d[1][0] + d[1][1], o_parts[0], o_parts[1]};
+      // The read-out of the token before is added up over the lanes together with this token's S^T k.
+      float dsum = (d0 + d1) + (d2 + d3), osum = o_parts;
 #pragma unroll
       for (int offset = 4; offset <= 16; offset <<= 1) {
-        float other[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, sums[i], offset);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sums[i] += other[i];
+        const float a = __shfl_xor_sync(0xffffffffu, dsum, offset), b = __shfl_xor_sync(0xffffffffu, osum, offset);
+        dsum += a;
+        osum += b;
       }
-      if (o_token >= 0 && part == 0)
-        *reinterpret_cast<float2*>(out + (size_t)o_token * heads * vdim + (size_t)head * vdim + column) =
-            make_float2(sums[2], sums[3]);
-      const float c[2] = {ga.x * (v[0] - sums[0] * ga.y), ga.x * (v[1] - sums[1] * ga.y)};
-      float o[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+      if (o_token >= 0 && part == 0) out[(size_t)o_token * heads * vdim + (size_t)head * vdim + column] = osum;
+      const float c = ga.x * (v - dsum * ga.y);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const float4 q4 = *reinterpret_cast<const float4*>(q + r);
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          S[x][r] = fmaf(S[x][r], ga.y, kk[r] * c[x]); S[x][r + 1] = fmaf(S[x][r + 1], ga.y, kk[r + 1] * c[x]);
-          S[x][r + 2] = fmaf(S[x][r + 2], ga.y, kk[r + 2] * c[x]); S[x][r + 3] = fmaf(S[x][r + 3], ga.y, kk[r + 3] * c[x]);
-          o[x][0] = fmaf(S[x][r], q4.x, o[x][0]); o[x][1] = fmaf(S[x][r + 1], q4.y, o[x][1]);
-          o[x][0] = fmaf(S[x][r + 2], q4.z, o[x][0]); o[x][1] = fmaf(S[x][r + 3], q4.w, o[x][1]);
-        }
+        S[r] = fmaf(S[r], ga.y, kk[r] * c); S[r + 1] = fmaf(S[r + 1], ga.y, kk[r + 1] * c);
+        S[r + 2] = fmaf(S[r + 2], ga.y, kk[r + 2] * c); S[r + 3] = fmaf(S[r + 3], ga.y, kk[r + 3] * c);
+        o0 = fmaf(S[r], q4.x, o0); o1 = fmaf(S[r + 1], q4.y, o1);
+        o2 = fmaf(S[r + 2], q4.z, o2); o3 = fmaf(S[r + 3], q4.w, o3);
       }
-      o_parts[0] = o[0][0] + o[0][1];
-      o_parts[1] = o[1][0] + o[1][1];
+      o_parts = (o0 + o1) + (o2 + o3);
       o_token = t0 + j;
     }
     __syncthreads();     // the buffer is written again two chunks on
   }
   {
-    const float o0 = sum_over_column_lanes(o_parts[0]), o1 = sum_over_column_lanes(o_parts[1]);
-    if (part == 0)
-      *reinterpret_cast<float2*>(out + (size_t)o_token * heads * vdim + (size_t)head * vdim + column) = make_float2(o0, o1);
+    const float o = sum_over_column_lanes(o_parts);
+    if (part == 0) out[(size_t)o_token * heads * vdim + (size_t)head * vdim + column] = o;
   }
 #pragma unroll
-  for (int x = 0; x < 2; ++x)
-#pragma unroll
-    for (int c = 0; c < R / 4; ++c)
-      *reinterpret_cast<float4*>(mine + x * dim + c * 4) =
-          make_float4(S[x][c * 4], S[x][c * 4 + 1], S[x][c * 4 + 2], S[x][c * 4 + 3]);
+  for (int c = 0; c < R / 4; ++c)
+    *reinterpret_cast<float4*>(mine + c * 4) = make_float4(S[c * 4], S[c * 4 + 1], S[c * 4 + 2], S[c * 4 + 3]);
 }
 
 template <typename T, int R>
@@ -507,9 +490,10 @@ int launch_delta_r(bool single, bool vector, int tokens, dim3 grid, cudaStream_t
     if (vector) LI_DELTA(1, true);
     LI_DELTA(1, false);
   }
-  if (vector && vdim % 32 == 0 && aligned16(scales) && (((size_t)heads * vdim) * sizeof(T)) % 16 == 0) {
-    constexpr size_t smem = 2 * (size_t)kStageTokens * (8 * 8 * R + 16 + 32 * sizeof(T));
-    return (int)launch_pdl(tokens, gated_delta_rule_staged_kernel<T, R>, grid, dim3(128), smem, stream, qkv, scales, gates,
+  if (vector && vdim % 16 == 0 && aligned16(scales) && (((size_t)heads * vdim) * sizeof(T)) % 16 == 0) {
+    constexpr size_t smem = 2 * (size_t)kStageTokens * (8 * 8 * R + 16 + (16 * sizeof(T) + 15) / 16 * 16);
+    const dim3 staged_grid(vdim / 16, grid.y, grid.z);
+    return (int)launch_pdl(tokens, gated_delta_rule_staged_kernel<T, R>, staged_grid, dim3(128), smem, stream, qkv, scales, gates,
                            state, qsl, slots, out, heads, kv_heads, vdim);
   }
   if (vector) LI_DELTA(kDeep, true);
