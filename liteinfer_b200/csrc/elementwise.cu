@@ -142,7 +142,7 @@ __global__ void add_bias_kernel(T* __restrict__ out, const T* __restrict__ bias,
 }
 
 // --------------------------------------------------------- gated activation
-constexpr int kSilu = 0, kGelu = 1, kGeluTanh = 2, kRelu = 3;
+constexpr int kSilu = 0, kGelu = 1, kGeluTanh = 2, kRelu = 3, kReluSquared = 4;
 
 __device__ __forceinline__ float activate(float x, int act) {
   switch (act) {
@@ -152,8 +152,30 @@ __device__ __forceinline__ float activate(float x, int act) {
       const float inner = 0.79788456080286535588f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.0f + tanhf(inner));
     }
+    case kReluSquared: {
+      const float r = fmaxf(x, 0.f);
+      return r * r;
+    }
     default: return fmaxf(x, 0.f);
   }
+}
+
+// out[i] = act(x[i]): the activation of a feed-forward that has no gate.
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n, int act) {
+  grid_dependency_wait();
+  grid_launch_dependents();
+  constexpr int N = Vec16<T>::N;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n / N; i += stride) {
+    const Vec16<T> v = load16(x + i * N);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < N; ++k) o.set(k, activate(v.get(k), act));
+    store16(out + i * N, o);
+  }
+  for (size_t i = (n / N) * N + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = from_float<T>(activate(to_float(x[i]), act));
 }
 
 // gate_up [rows, 2*width]: gate in the first `width` columns, up in the rest.
@@ -380,4 +402,19 @@ LI_EXPORT int li_act_mul_interleaved(int dtype, const void* gate_up, void* out, 
     act_mul_interleaved_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows,
                                                                           width, act);
   LI_LAUNCH_CHECK();
+}
+
+// out[i] = act(x[i]) over n elements (in place when out == x); act as in li_act_mul, and 4: the square of relu.
+LI_EXPORT int li_activation(int dtype, const void* x, void* out, size_t n, int act, cudaStream_t stream) {
+  if (act < 0 || act > 4) return LI_ERR_UNSUPPORTED;
+  if (n == 0) return 0;
+  if (!aligned16(x) || !aligned16(out)) return LI_ERR_ALIGNMENT;
+  const size_t vectors = n / (dtype == kFloat32 ? 4 : 8) + 1;
+  const int blocks = (int)(vectors / 256 + 1 < 148 * 8 ? vectors / 256 + 1 : 148 * 8);
+  cudaError_t e;
+  if (dtype == kFloat32)
+    e = launch_pdl((long)n, activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, act);
+  else
+    e = launch_pdl((long)n, activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n, act);
+  return (int)e;
 }

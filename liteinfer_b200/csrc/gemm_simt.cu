@@ -15,10 +15,13 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ out,
-                 int M, int N, int K) {
+                 int M, int N, int K, int ldx, int ldo, long x_batch, long w_batch, long out_batch) {
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  x += blockIdx.z * x_batch;        // one product per blockIdx.z (a plain product is a batch of one)
+  w += blockIdx.z * w_batch;
+  out += blockIdx.z * out_batch;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
   float acc[4][4];
 #pragma unroll
@@ -33,7 +36,7 @@ gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __re
     for (int i = 0; i < 4; ++i) {
       const int k = k0 + lk + i;
       const int m = m0 + lr, n = n0 + lr;
-      xs[lk + i][lr] = (m < M && k < K) ? to_float(x[(size_t)m * K + k]) : 0.f;
+      xs[lk + i][lr] = (m < M && k < K) ? to_float(x[(size_t)m * ldx + k]) : 0.f;
       ws[lk + i][lr] = (n < N && k < K) ? to_float(w[(size_t)n * K + k]) : 0.f;
     }
     __syncthreads();
@@ -61,7 +64,7 @@ gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __re
       if (n >= N) continue;
       float v = acc[i][j];
       if (bias) v += to_float(bias[n]);
-      out[(size_t)m * N + n] = from_float<T>(v);
+      out[(size_t)m * ldo + n] = from_float<T>(v);
     }
   }
 }
@@ -77,9 +80,26 @@ LI_EXPORT int li_gemm_simt(int dtype, const void* x, const void* w, const void* 
   if (grid.y > 65535) return LI_ERR_UNSUPPORTED;
   if (dtype == kFloat32)
     gemm_simt_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, (const float*)bias,
-                                                      (float*)out, M, N, K);
+                                                      (float*)out, M, N, K, K, N, 0, 0, 0);
   else
     gemm_simt_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M,
-                                                     N, K);
+                                                     N, K, K, N, 0, 0, 0);
+  LI_LAUNCH_CHECK();
+}
+
+// A batch of products: out[b][m][n] = sum_k x[b][m][k] * w[b][n][k], b < batch.  x[b] starts at x + b * x_batch
+// with `ldx` elements between its rows, w[b] at w + b * w_batch (rows of K), out[b] at out + b * out_batch with
+// `ldo` between rows: operands may be slices of wider tensors (a head's columns of a projection).
+LI_EXPORT int li_gemm_simt_batched(int dtype, const void* x, const void* w, void* out, int M, int N, int K, int batch,
+                                   int ldx, int ldo, long x_batch, long w_batch, long out_batch, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || batch > 65535) return LI_ERR_UNSUPPORTED;
+  if (dtype == kFloat32)
+    gemm_simt_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, nullptr, (float*)out, M, N, K,
+                                                      ldx, ldo, x_batch, w_batch, out_batch);
+  else
+    gemm_simt_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, nullptr, (bf16*)out, M, N, K, ldx,
+                                                     ldo, x_batch, w_batch, out_batch);
   LI_LAUNCH_CHECK();
 }

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_long, c_size_t, c_void_p
 
 from dataclasses import dataclass
 
@@ -22,6 +22,8 @@ from liteinfer_b200.ops.library import KernelLibraryError, load
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "gelu_tanh": 2, "relu": 3}
+# Activations of a feed-forward without a gate (`activation`): the above, and the square of relu.
+UNARY_ACTIVATIONS = {**ACTIVATIONS, "relu_squared": 4}
 
 _ERRORS = {
     100001: "the kernel refuses these sizes (unsupported shape or option)",
@@ -89,6 +91,21 @@ _SIGNATURES = {
     "li_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "li_gemm_simt_batched": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_long, c_long, c_long, c_void_p]),
+    "li_activation": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "li_embedding_streams": ("stream_mix", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                                            c_void_p, c_void_p]),
+    "li_stream_rmsnorm": ("stream_mix", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "li_latent_prep": ("attention_latent", [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                            c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_int, c_int, c_void_p, c_int, c_void_p]),
+    "li_latent_attention": ("attention_latent", [c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
+                                                 c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_int, c_float, c_void_p]),
+    "li_gate_heads": ("attention_latent", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p]),
     "li_sample": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -1051,6 +1068,167 @@ def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, d
     if max_query_len != 1:
         global launch_count
         launch_count += 1   # two kernels
+    return out
+
+
+# ------------------------------------------- several residual streams, latent attention
+@dataclass
+class StreamUpdate:
+    """A rewrite of the residual streams that has not been done yet: stream t becomes sum_s mix[s, t] * stream s +
+    write[t] * gain * value, all from the old streams (`value` [tokens, width] is a sublayer's output in the
+    engine's dtype; gain [width], write [S] and mix [S, S], indexed [from, to], are float32; gain None = ones).
+    The norm that reads the streams next does the rewrite on its way (`stream_rmsnorm`)."""
+
+    value: torch.Tensor
+    gain: torch.Tensor | None
+    write: torch.Tensor
+    mix: torch.Tensor
+
+
+def embedding_streams(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+                      error_flag: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, s * width:(s + 1) * width] = float32(table[ids[t]]) * scale for every copy s (out float32
+    [tokens, copies * width]): the start of a 32-bit residual of one or several streams."""
+    _on_gpu(ids, table, out, error_flag)
+    _int32(ids, "ids"); _int32(error_flag, "error_flag")
+    tokens, width = ids.numel(), table.shape[1]
+    assert out.dtype == torch.float32 and out.shape[0] == tokens and out.shape[1] % width == 0
+    _check(_fn("li_embedding_streams")(_code(table), ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, width,
+                                       table.shape[0], float(scale), out.shape[1] // width, _ptr(error_flag),
+                                       _stream()), "embedding_streams")
+    return out
+
+
+def stream_rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                   read: torch.Tensor | None = None, update: StreamUpdate | None = None,
+                   rows: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor | None:
+    """The pending rewrite of the streams (`update`, stored back into x unless `rows` is given), then
+    out[r] = u / sqrt(mean(u^2) + eps) * weight * out_scale with u = sum_s read[s] * stream s of row rows[r] (or r);
+    read None sums the streams.  x float32 [tokens, S * width]; weight float32 [width]; out [n, width] in the
+    engine's dtype, None: only the rewrite is done.  Everything in between is 32-bit."""
+    _on_gpu(x, weight, out, read, rows, update.value if update else None, update.gain if update else None,
+            update.write if update else None, update.mix if update else None)
+    _int32(rows, "rows")
+    assert x.dtype == torch.float32 and (weight is None) == (out is None)
+    if out is not None:
+        width, n = out.shape[1], out.shape[0]
+        assert weight.dtype == torch.float32 and weight.numel() == width
+        dtype = out.dtype
+    else:
+        width, n, dtype = update.value.shape[1], x.shape[0], update.value.dtype
+    S = x.shape[1] // width
+    assert x.shape[1] == S * width and (rows is None or rows.numel() == n) and (rows is not None or n == x.shape[0])
+    assert read is None or (read.dtype == torch.float32 and read.numel() == S)
+    if update is not None:
+        assert update.value.shape == (x.shape[0], width) and update.value.dtype == dtype
+        assert update.write.dtype == update.mix.dtype == torch.float32
+        assert update.write.numel() == S and update.mix.shape == (S, S)
+        assert update.gain is None or (update.gain.dtype == torch.float32 and update.gain.numel() == width)
+    _check(_fn("li_stream_rmsnorm")(
+        _DTYPE_CODE[dtype], x.data_ptr(), _ptr(update.value if update else None), _ptr(update.gain if update else None),
+        _ptr(update.write if update else None), _ptr(update.mix if update else None), _ptr(read), _ptr(weight),
+        _ptr(out), _ptr(rows), n, width, S, float(eps), float(out_scale), int(update is not None and rows is None),
+        _stream()), "stream_rmsnorm")
+    return out
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, name: str) -> torch.Tensor:
+    """out = act(x) element by element (out may be x); `name` from UNARY_ACTIVATIONS."""
+    _on_gpu(x, out)
+    assert x.shape == out.shape and x.dtype == out.dtype
+    if name not in UNARY_ACTIVATIONS:
+        raise KernelLibraryError(f"activation {name!r} has no kernel; known: {sorted(UNARY_ACTIVATIONS)}")
+    _check(_fn("li_activation")(_code(x), x.data_ptr(), out.data_ptr(), x.numel(), UNARY_ACTIVATIONS[name], _stream()),
+           "activation")
+    return out
+
+
+def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = x[b] @ weight[b]^T for every b: x [B, M, K] (any batch and row strides, contiguous k: a head's
+    columns of a projection), weight [B, N, K] contiguous, out [B, M, N] contiguous.  float32 runs the FFMA kernel,
+    bfloat16 the library's batched product (32-bit accumulation)."""
+    _on_gpu(weight, out)
+    B, M, K = x.shape
+    N = weight.shape[1]
+    assert weight.shape == (B, N, K) and out.shape == (B, M, N) and x.dtype == weight.dtype == out.dtype
+    if not x.is_cuda:
+        raise KernelLibraryError(f"liteinfer_b200 kernels run on a CUDA device only; there is no CPU path (got {x.device})")
+    if K > 1 and x.stride(2) != 1:
+        raise KernelLibraryError("batched_linear takes x with contiguous rows")
+    if M == 0:
+        return out
+    if x.dtype == torch.float32:
+        _check(_fn("li_gemm_simt_batched")(0, x.data_ptr(), weight.data_ptr(), out.data_ptr(), M, N, K, B, x.stride(1),
+                                           N, x.stride(0), N * K, M * N, _stream()), "gemm_simt_batched")
+        return out
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+    return out
+
+
+def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, kv_off: int | None, kv_rank: int, rot_dim: int,
+                rot_dims: int, q_weight: torch.Tensor, kv_weight: torch.Tensor | None, eps: float,
+                inv_freq: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                block_table: torch.Tensor, pool: torch.Tensor, q_out: torch.Tensor, store: bool = True) -> None:
+    """Per token of `proj` [tokens, columns]: q_out = rmsnorm(proj[:, q_off:q_off + q_rank]) * q_weight, and, with
+    `kv_off` and `store`, the token's cache entry pool[page, slot] = [rmsnorm(latent) * kv_weight | rotated key
+    part], latent = proj[:, kv_off:kv_off + kv_rank], the key part the rot_dim columns behind it, of which the
+    first `rot_dims` turn by position * inv_freq (pairs i, i + rot_dims / 2).  pool [pages, 1, page_size, kv_rank +
+    rot_dim]; norm weights float32; tokens whose sequence is -1 store nothing."""
+    _on_gpu(proj, q_weight, kv_weight, inv_freq, positions, seq_of_token, block_table, pool, q_out)
+    _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
+    tokens = proj.shape[0]
+    pages, one, page_size, entry = pool.shape
+    assert one == 1 and entry == kv_rank + rot_dim and pool.dtype == proj.dtype == q_out.dtype
+    assert q_out.shape == (tokens, q_rank) and q_weight.dtype == torch.float32 and q_weight.numel() == q_rank
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dims
+    writes = kv_off is not None and store
+    assert not writes or (kv_weight.dtype == torch.float32 and kv_weight.numel() == kv_rank)
+    _check(_fn("li_latent_prep")(_code(proj), proj.data_ptr(), proj.stride(0), q_off, q_rank, kv_off if writes else -1,
+                                 kv_rank, rot_dim, rot_dims, q_weight.data_ptr(), _ptr(kv_weight if writes else None),
+                                 float(eps), inv_freq.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
+                                 block_table.data_ptr(), block_table.stride(0), pool.data_ptr(), page_size,
+                                 pages if writes else 0, q_out.data_ptr(), tokens, _stream()), "latent_prep")
+
+
+def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: int, q_rot_off: int, out: torch.Tensor,
+                     pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
+                     context_lens: torch.Tensor, inv_freq: torch.Tensor, sink: torch.Tensor | None, num_seqs: int,
+                     max_q_len: int, heads: int, kv_rank: int, rot_dim: int, rot_dims: int, scale: float,
+                     plan=None) -> torch.Tensor:
+    """Causal multi-query attention of every head over the shared cache entries [latent | rotated key part]:
+    score = (q_lat . latent + rotate(q_rot) . key part) * scale, out = sum_j p_j latent_j, with exp(sink[h]) as one
+    more term of the softmax's denominator (sink float32 [heads] or None).  q_lat, out: [heads, tokens, kv_rank];
+    q_raw [tokens, columns]: the part of head h that turns lies at columns h * q_head_stride + q_rot_off (rot_dim
+    numbers, rotated here by the query's position).  pool [pages, 1, page_size, kv_rank + rot_dim]."""
+    _on_gpu(q_lat, q_raw, out, pool, block_table, query_start_loc, context_lens, inv_freq, sink)
+    _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
+    pages, one, page_size, entry = pool.shape
+    tokens = q_raw.shape[0]
+    assert one == 1 and entry == kv_rank + rot_dim and q_lat.shape == out.shape == (heads, tokens, kv_rank)
+    assert q_lat.dtype == q_raw.dtype == out.dtype == pool.dtype
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads)
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dims
+    _check(_fn("li_latent_attention")(
+        _code(q_raw), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_raw.data_ptr(), q_raw.stride(0),
+        q_head_stride, q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), inv_freq.data_ptr(), _ptr(sink),
+        num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages, float(scale), _stream()),
+        "latent_attention")
+    return out
+
+
+def gate_heads(v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """out[t, h * e:(h + 1) * e] = v[h, t] * sigmoid(gate[t, h * e:(h + 1) * e]): v [heads, tokens, e] head-major,
+    gate [tokens, heads * e] (a column slice is fine; None: no gate, only the transposition), out [tokens, heads *
+    e]; the sigmoid is 32-bit."""
+    _on_gpu(v, out)
+    heads, tokens, e = v.shape
+    assert out.shape == (tokens, heads * e) and v.dtype == out.dtype
+    if gate is not None:
+        _rows2d(gate, "gate")
+        assert gate.shape == out.shape and gate.dtype == v.dtype
+    _check(_fn("li_gate_heads")(_code(v), v.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                out.data_ptr(), tokens, heads, e, _stream()), "gate_heads")
     return out
 
 

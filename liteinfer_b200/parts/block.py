@@ -33,7 +33,7 @@ def apply_norm(norm, hidden: torch.Tensor, delta, consumer=None, rows: torch.Ten
     """Runs `norm` on the residual stream, whatever form the pending `delta` has (None, a tensor still to be
     added, or `ops.RowStats` of a sum already made), using what the norm and the part that reads its result say
     they can do: a norm that `defers` hands a consumer that `takes_pending_norm` the unfinished norm."""
-    if isinstance(delta, ops.NormedDelta):
+    if isinstance(delta, (ops.NormedDelta, ops.StreamUpdate)):
         return norm.forward(hidden, delta) if rows is None else norm.forward(hidden, delta, rows=rows)
     if isinstance(delta, ops.RowStats) and not getattr(norm, "reads_row_stats", False):
         delta = None                # the sum is in `hidden` already; a plain norm needs no more
@@ -102,6 +102,43 @@ class SandwichNormMixerBlock(SandwichNormBlock):
     roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm"}
 
 
+class StreamMixedBlock:
+    """A pre-norm block whose residual is one or several 32-bit streams (parts/connection.py): every sublayer
+    reads the streams through its connection's coefficients, and its output, scaled per channel, rewrites all
+    streams through the connection's small matrix:
+
+        u = sum_s read[s] x_s;  y = sublayer(norm(u));  x_t <- sum_s mix[s, t] x_s + write[t] * gain * y
+
+    The rewrite travels as an `ops.StreamUpdate`; the norm that reads the streams next (this block's second, the
+    next block's first, the model's last) does it on its way, so the streams are read and written once per
+    sublayer.  A layer may have no feed-forward."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_connection": "connection", "feed_forward_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_connection": "connection"}
+
+    def __init__(self, parts: dict) -> None:
+        self.mixer_norm, self.mixer, self.mixer_connection = parts["mixer_norm"], parts["mixer"], parts["mixer_connection"]
+        self.feed_forward_norm = parts.get("feed_forward_norm")
+        self.feed_forward = parts.get("feed_forward")
+        self.feed_forward_connection = parts.get("feed_forward_connection")
+
+    def forward(self, hidden: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        normed = self.mixer_norm.forward(hidden, delta, read=self.mixer_connection.read)
+        delta = self.mixer_connection.update(self.mixer.forward(normed, ctx, cache))
+        if self.feed_forward is None:
+            return hidden, delta
+        normed = self.feed_forward_norm.forward(hidden, delta, read=self.feed_forward_connection.read)
+        return hidden, self.feed_forward_connection.update(self.feed_forward.forward(normed, ctx))
+
+
+class StreamMixedMixerBlock(StreamMixedBlock):
+    """`StreamMixedBlock` of a layer that has no feed-forward."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_connection": "connection"}
+
+
 register_block("prenorm_residual", PreNormResidualBlock)
+register_block("stream_mixed", StreamMixedBlock)
+register_block("stream_mixed_mixer_only", StreamMixedMixerBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("sandwich_norm_mixer_only", SandwichNormMixerBlock)

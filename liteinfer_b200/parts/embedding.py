@@ -14,10 +14,13 @@ from liteinfer_b200.parts.spec import TensorSpec
 
 
 class TokenEmbedding:
-    """h[t] = table[token[t]] — liteinfer/models/llama.py:204,217."""
+    """h[t] = table[token[t]] — liteinfer/models/llama.py:204,217.  `scale` multiplies every row; a model whose
+    residual is 32-bit streams starts them with `forward_streams`, where the row is widened before the multiply."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: torch.device,
+                 scale: float = 1.0) -> None:
         self.vocab_size, self.hidden_size, self.dtype, self.device = vocab_size, hidden_size, dtype, device
+        self.scale = float(scale)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
@@ -30,7 +33,14 @@ class TokenEmbedding:
         out = torch.empty((token_ids.numel(), self.hidden_size), dtype=self.weight.dtype, device=token_ids.device)
         # An id outside the table gives a zero row and raises the device's token flag, which
         # `ModelRunner.check_kernels` reports (the step function refuses such ids on the host before that).
+        if self.scale != 1.0:
+            raise ValueError("a scaled embedding starts 32-bit streams (forward_streams); it has no output of the engine's dtype")
         return ops.embedding(token_ids, self.weight, out, ops.token_error_flag(token_ids.device))
+
+    def forward_streams(self, token_ids: torch.Tensor, copies: int) -> torch.Tensor:
+        """[tokens, copies * hidden] float32: `copies` equal streams, each table[token] * scale."""
+        out = torch.empty((token_ids.numel(), copies * self.hidden_size), dtype=torch.float32, device=token_ids.device)
+        return ops.embedding_streams(token_ids, self.weight, out, self.scale, ops.token_error_flag(token_ids.device))
 
 
 class LinearHead:

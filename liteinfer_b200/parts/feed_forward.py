@@ -75,4 +75,29 @@ class GatedMLP:
         return ops.linear(hidden, self.down_weight, None, self.down_bias, residual=residual)
 
 
+class DenseMLP:
+    """down(act(up(x))): a feed-forward without a gate; `activation` from `ops.UNARY_ACTIVATIONS`
+    ("relu_squared": the square of relu)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, dtype: torch.dtype,
+                 device: torch.device) -> None:
+        if activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} has no kernel; known: {sorted(ops.UNARY_ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.up_weight = self.down_weight = None
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        i, h = self.intermediate_size, self.hidden_size
+        return {"up_proj.weight": TensorSpec((i, h)), "down_proj.weight": TensorSpec((h, i))}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.up_weight, self.down_weight = tensors["up_proj.weight"], tensors["down_proj.weight"]
+
+    def forward(self, x, ctx: StepContext):
+        hidden = ops.linear(x, self.up_weight, None)
+        ops.activation(hidden, hidden, self.activation)
+        return ops.linear(hidden, self.down_weight, None)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("dense_mlp", DenseMLP)

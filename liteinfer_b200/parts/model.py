@@ -13,9 +13,11 @@ import torch
 
 import liteinfer_b200.parts.attention  # noqa: F401  (registers the built-in parts)
 import liteinfer_b200.parts.block  # noqa: F401
+import liteinfer_b200.parts.connection  # noqa: F401
 import liteinfer_b200.parts.delta_rule  # noqa: F401
 import liteinfer_b200.parts.embedding  # noqa: F401
 import liteinfer_b200.parts.feed_forward  # noqa: F401
+import liteinfer_b200.parts.latent_attention  # noqa: F401
 import liteinfer_b200.parts.norm  # noqa: F401
 import liteinfer_b200.parts.position  # noqa: F401
 import liteinfer_b200.parts.reentry  # noqa: F401
@@ -25,9 +27,14 @@ from liteinfer_b200.parts.context import LayerCache, StepContext
 from liteinfer_b200.parts.registry import BLOCKS, build_part
 from liteinfer_b200.parts.spec import ModelSpec, TensorSpec
 
-def _settled(hidden: torch.Tensor, delta) -> torch.Tensor:
-    """A copy of the residual stream with the pending delta added (for `StepContext.layer_trace`)."""
+def _settled(hidden: torch.Tensor, delta, copies: int | None = None) -> torch.Tensor:
+    """A copy of the residual stream with the pending delta added (for `StepContext.layer_trace`); of a residual
+    kept as several streams, their sum."""
     out = hidden.clone()
+    if copies is not None:
+        if isinstance(delta, ops.StreamUpdate):
+            ops.stream_rmsnorm(out, None, 0.0, None, update=delta)
+        return out.view(out.shape[0], copies, -1).sum(1)
     if isinstance(delta, ops.NormedDelta):
         ops.layernorm_add(out, delta.value, delta.weight, delta.eps)
     elif isinstance(delta, torch.Tensor):
@@ -68,7 +75,7 @@ class Model:
         self.reentry = (build_part("reentry", spec.reentry, dtype=dtype, device=device)
                         if spec.reentry is not None else None)
         self.schedule = spec.schedule
-        self.wide_stream = spec.stream_dtype == "float32" and dtype != torch.float32
+        self.wide_stream = spec.stream_dtype == "float32" and dtype != torch.float32 and spec.stream_copies is None
 
     # ------------------------------------------------------------- tensors
     def _named_parts(self):
@@ -121,7 +128,11 @@ class Model:
     # ------------------------------------------------------------- forward
     def hidden(self, ctx: StepContext, caches: list[LayerCache]) -> tuple[torch.Tensor, torch.Tensor | None]:
         """Runs the schedule; returns the residual stream and the delta still to be added."""
-        embedded = hidden = self.embedding.forward(ctx.token_ids)
+        if self.spec.stream_copies is not None:
+            # The residual is 32-bit streams: the embedding widens its rows itself and writes every copy.
+            embedded, hidden = None, self.embedding.forward_streams(ctx.token_ids, self.spec.stream_copies)
+        else:
+            embedded = hidden = self.embedding.forward(ctx.token_ids)
         if self.wide_stream:
             # The stream is summed in 32-bit: the embedding's rows are widened once, every layer adds in place.
             hidden = ops.convert(embedded, torch.empty(embedded.shape, dtype=torch.float32, device=embedded.device))
@@ -133,7 +144,7 @@ class Model:
                 hidden, delta = self.reentry.forward(hidden, delta, embedded)
             hidden, delta = self.layers[entry.layer].block.forward(hidden, delta, ctx, caches[stop])
             if ctx.layer_trace is not None:
-                ctx.layer_trace.append(_settled(hidden, delta))
+                ctx.layer_trace.append(_settled(hidden, delta, self.spec.stream_copies))
         return hidden, delta
 
     def forward(self, ctx: StepContext, caches: list[LayerCache]) -> torch.Tensor:

@@ -91,5 +91,37 @@ class LayerNorm:
         return ops.NormedDelta(value, self.weight, self.eps)
 
 
+class StreamRMSNorm:
+    """y = u / sqrt(mean(u^2) + eps) * weight * out_scale, all in 32-bit, of a residual kept as `streams` 32-bit
+    copies side by side in a row: u = sum_s read[s] * stream s (`read` None: the plain sum; with one stream, the
+    stream).  `delta` may be an `ops.StreamUpdate`, the rewrite of the streams that the sublayer before left
+    pending: the same kernel does it on its way (and stores it, unless only `rows` are asked for).  The result has
+    the engine's dtype; the weight is kept 32-bit.  `out_scale`: a constant folded into the result (a model that
+    scales its logits gives it to its last norm)."""
+
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device, streams: int = 1,
+                 out_scale: float = 1.0) -> None:
+        self.size, self.eps, self.dtype, self.device = size, float(eps), dtype, device
+        self.streams, self.out_scale = int(streams), float(out_scale)
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.size,), kind="f32", init="ones_normal")}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"].contiguous()
+
+    def forward(self, x: torch.Tensor, delta: "ops.StreamUpdate | None" = None, rows: torch.Tensor | None = None,
+                out: torch.Tensor | None = None, read: torch.Tensor | None = None) -> torch.Tensor:
+        if delta is not None and not isinstance(delta, ops.StreamUpdate):
+            raise TypeError("a norm over residual streams takes a pending ops.StreamUpdate, not a plain delta")
+        n = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
+        return ops.stream_rmsnorm(x, self.weight, self.eps, out, read=read, update=delta, rows=rows,
+                                  out_scale=self.out_scale)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("stream_rmsnorm", StreamRMSNorm)
 register_norm("layernorm", LayerNorm)

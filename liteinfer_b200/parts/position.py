@@ -79,16 +79,23 @@ def yarn_inverse_frequencies(dims: int, theta: float, factor: float, original: f
 
 class RotaryEmbedding:
     """Half-split rotary embedding: dimension j pairs with j + rotary_dim/2 (llama.py:89-102).  `rope_type`
-    "yarn" takes `factor`, `original_max_position_embeddings`, `fast` and `slow` (`yarn_inverse_frequencies`)."""
+    "yarn" takes `factor`, `original_max_position_embeddings`, `fast` and `slow` (`yarn_inverse_frequencies`).
+    `exact`: the plain frequencies computed in 64-bit and rounded once, instead of in 32-bit as the reference does."""
 
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rotary_dim: int | None = None, rope_type: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
                  original_max_position_embeddings: float = 0, fast: float | None = None,
-                 slow: float | None = None) -> None:
+                 slow: float | None = None, exact: bool = False) -> None:
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         scale = 1.0
-        if rope_type == "yarn":
+        if exact:
+            # theta^(-2i/d) in 64-bit, rounded once (the plain frequencies only).
+            if rope_type != "default":
+                raise ValueError("exact frequencies are the plain ones (rope_type 'default')")
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            inv_freq = (float(theta) ** (-2.0 * i / self.rotary_dim)).to(torch.float32)
+        elif rope_type == "yarn":
             if fast is None or slow is None or not original_max_position_embeddings > 0:
                 raise ValueError("yarn scaling needs factor, original_max_position_embeddings, fast and slow")
             inv_freq, scale = yarn_inverse_frequencies(self.rotary_dim, theta, factor,

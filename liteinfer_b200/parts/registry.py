@@ -18,10 +18,11 @@ BLOCKS: dict[str, Callable[..., Any]] = {}
 EMBEDDINGS: dict[str, Callable[..., Any]] = {}
 HEADS: dict[str, Callable[..., Any]] = {}
 REENTRIES: dict[str, Callable[..., Any]] = {}
+CONNECTIONS: dict[str, Callable[..., Any]] = {}
 
 _TABLES = {
     "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS,
-    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "reentry": REENTRIES,
+    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "reentry": REENTRIES, "connection": CONNECTIONS,
 }
 
 
@@ -61,6 +62,10 @@ def register_head(kind: str, factory, replace: bool = False) -> None:
 
 def register_reentry(kind: str, factory, replace: bool = False) -> None:
     _register(REENTRIES, "re-entry part", kind, factory, replace)
+
+
+def register_connection(kind: str, factory, replace: bool = False) -> None:
+    _register(CONNECTIONS, "connection", kind, factory, replace)
 
 
 def build_part(role: str, spec, **context):

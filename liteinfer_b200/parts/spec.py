@@ -90,6 +90,10 @@ class ModelSpec:
     # "float32": the residual stream is kept in 32-bit whatever the engine's dtype (the embedding's output is
     # widened, the norms read and write it in 32-bit); None: it has the engine's dtype.
     stream_dtype: str | None = None
+    # A number n: the residual of a token is n 32-bit streams side by side in one row [n * hidden_size], started by
+    # the embedding's `forward_streams` (n equal copies) and read by norms that know streams (`stream_rmsnorm`);
+    # None: one residual of hidden_size numbers.
+    stream_copies: int | None = None
     # A part that mixes the embedding's output back into the stream before the stops marked `reenter`.
     reentry: PartSpec | None = None
     reentry_prefix: str = ""
@@ -104,6 +108,8 @@ class ModelSpec:
             raise ValueError("a model's schedule names no layer")
         if self.stream_dtype not in (None, "float32"):
             raise ValueError(f"stream_dtype {self.stream_dtype!r} is not supported; known: None, 'float32'")
+        if self.stream_copies is not None and (self.stream_copies < 1 or self.reentry is not None):
+            raise ValueError("stream_copies must be >= 1, and a model with residual streams has no reentry part")
         for stop, entry in enumerate(self.schedule):
             if entry.reenter and self.reentry is None:
                 raise ValueError(f"stop {stop} re-enters the stream, but the model names no reentry part")

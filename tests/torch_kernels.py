@@ -376,10 +376,125 @@ def sample(logits, temperature, top_k, top_p, uniform, out):
     return out
 
 
+# ------------------------------------------------- residual streams, latent attention
+def embedding_streams(ids, table, out, scale=1.0, error_flag=None):
+    bad = (ids < 0) | (ids >= table.shape[0])
+    rows = table[ids.long().clamp(0, table.shape[0] - 1)].float() * scale
+    rows[bad] = 0
+    if error_flag is not None and bool(bad.any()):
+        error_flag.fill_(1)
+    out.copy_(rows.repeat(1, out.shape[1] // table.shape[1]))
+    return out
+
+
+def stream_rmsnorm(x, weight, eps, out, read=None, update=None, rows=None, out_scale=1.0):
+    width = out.shape[1] if out is not None else update.value.shape[1]
+    T, S = x.shape[0], x.shape[1] // width
+    streams = x.view(T, S, width)
+    if update is not None:
+        add = update.value.float() * (update.gain if update.gain is not None else 1.0)
+        streams = torch.einsum("st,nsd->ntd", update.mix, streams) + update.write[None, :, None] * add[:, None, :]
+        if rows is None:
+            x.copy_(streams.reshape(T, S * width))
+    if out is None:
+        return None
+    if rows is not None:
+        streams = streams[rows.long()]
+    u = streams.sum(1) if read is None else torch.einsum("s,nsd->nd", read, streams)
+    out.copy_((u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight * out_scale).to(out.dtype))
+    return out
+
+
+def activation(x, out, name):
+    v = x.float()
+    out.copy_((torch.relu(v) ** 2 if name == "relu_squared" else _activate(v, name)).to(out.dtype))
+    return out
+
+
+def batched_linear(x, weight, out):
+    out.copy_(torch.einsum("bmk,bnk->bmn", x.float(), weight.float()).to(out.dtype))
+    return out
+
+
+def _turn(x, positions, inv_freq, dims):
+    """Half-split rotation of the first `dims` numbers of the last axis of x [T, ..., n]."""
+    half = dims // 2
+    angle = positions.float()[:, None] * inv_freq.float()[None, :]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+    cos, sin = angle.cos().reshape(shape), angle.sin().reshape(shape)
+    a, b = x[..., :half], x[..., half:dims]
+    return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., dims:]), dim=-1)
+
+
+def latent_prep(proj, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_weight, kv_weight, eps, inv_freq, positions,
+                seq_of_token, block_table, pool, q_out, store=True):
+    dtype = proj.dtype
+    page_size = pool.shape[2]
+    q = proj[:, q_off:q_off + q_rank].float()
+    q_out.copy_((q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight).to(dtype))
+    if kv_off is None or not store:
+        return
+    latent = proj[:, kv_off:kv_off + kv_rank].float()
+    latent = latent / torch.sqrt(latent.pow(2).mean(-1, keepdim=True) + eps) * kv_weight
+    shared = _turn(proj[:, kv_off + kv_rank:kv_off + kv_rank + rot_dim].float(), positions, inv_freq, rot_dims)
+    entries = torch.cat([latent, shared], dim=-1).to(dtype)
+    tables = block_table.tolist()
+    for t, (seq, pos) in enumerate(zip(seq_of_token.tolist(), positions.tolist())):
+        if seq < 0:
+            continue
+        page = tables[seq][pos // page_size]
+        if 0 <= page < pool.shape[0]:
+            pool[page, 0, pos % page_size] = entries[t]
+
+
+def latent_attention(q_lat, q_raw, q_head_stride, q_rot_off, out, pool, block_table, query_start_loc, context_lens,
+                     inv_freq, sink, num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, scale, plan=None):
+    dtype = out.dtype
+    page_size = pool.shape[2]
+    qsl, ctx = query_start_loc.tolist(), context_lens.tolist()
+    slots_of = addressing.slot_table(block_table.tolist()[:num_seqs], [max(c, 0) for c in ctx[:num_seqs]], page_size,
+                                     q_raw.device)
+    flat = pool[:, 0].reshape(-1, kv_rank + rot_dim).float()
+    tokens = q_raw.shape[0]
+    q_rot_all = q_raw[:, :heads * q_head_stride].float().view(tokens, heads, q_head_stride)[:, :, q_rot_off:q_rot_off + rot_dim]
+    for s in range(num_seqs):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n, c = q1 - q0, ctx[s]
+        if n == 0:
+            continue
+        qpos = torch.arange(c - n, c, device=q_raw.device)
+        q_rot = _r(_turn(q_rot_all[q0:q1], qpos, inv_freq, rot_dims), dtype)          # [n, H, r]
+        q = torch.cat([q_lat[:, q0:q1].float(), q_rot.transpose(0, 1)], dim=-1)           # [H, n, c + r]
+        slots = slots_of[s, :c]
+        entries = flat[slots.clamp(min=0)]
+        scores = torch.einsum("hqd,kd->hqk", q, entries) * scale
+        hidden = (torch.arange(c, device=q_raw.device)[None, :] > qpos[:, None]) | (slots < 0)[None, :]
+        scores = scores.masked_fill(hidden[None], float("-inf"))
+        m = scores.amax(-1, keepdim=True)
+        if sink is not None:
+            m = torch.maximum(m, sink[:, None, None])
+        p = torch.exp(scores - m)
+        denom = p.sum(-1, keepdim=True)
+        if sink is not None:
+            denom = denom + torch.exp(sink[:, None, None] - m)
+        out[:, q0:q1] = (torch.einsum("hqk,kd->hqd", _r(p, dtype), entries[:, :kv_rank]) / denom).to(dtype)
+    return out
+
+
+def gate_heads(v, gate, out):
+    heads, tokens, e = v.shape
+    joined = v.float().transpose(0, 1).reshape(tokens, heads * e)
+    if gate is not None:
+        joined = joined * torch.sigmoid(gate.float())
+    out.copy_(joined.to(out.dtype))
+    return out
+
+
 def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
+ALL = ("embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
+       "gate_heads", "convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
        "short_conv", "short_conv_step", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
