@@ -14,6 +14,7 @@ decode at batch 1 and 64.  Weights are random (seeded) and token ids synthetic.
 
 `--compare kegizen` prints another line instead (the default run is unchanged): prefill and decode of the Kegizen
 decoder beside the Llama decoder at equal layer sizes, and the Kegizen kernels one by one beside their like.
+`--compare gifudra` does the same for the Gifudra decoder (latent attention, residual streams).
 """
 
 from __future__ import annotations
@@ -435,10 +436,115 @@ def _kegizen_kernels(peaks: dict) -> dict:
     return {k: round(v, 4) for k, v in out.items()}
 
 
-def run_kegizen(args) -> dict:
-    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 near a context of 2,048) of a Kegizen model
-    and of a Llama model with the same width, depth, head sizes and feed-forward, random weights, bfloat16; and
-    the design's kernels one by one.  Printed as one JSON line; the default run of this file does not include it."""
+def _gifudra_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int) -> dict:
+    """Latent attention with as many heads as the Llama layer has at head size 128 (unrotated part 128, rotated
+    part 64, values 128, a query latent of three quarters of the width, a key/value latent of 512), four residual
+    streams, a squared-relu feed-forward as wide as the Llama layer's; every fourth layer reads the cache entries of
+    the layer before it."""
+    h = heads * head_dim // 128
+    mixer = {"heads": h, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width * 3 // 4, "kv_rank": 512,
+             "scale": 192 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}
+    return {"architecture": "Gifudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
+            "logit_scale": 0.5, "streams": 4,
+            "layers": [{"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+                        "mixer": dict(mixer, kv_from=i - 1) if i % 4 == 3 else mixer} for i in range(layers)]}
+
+
+def _gifudra_kernels(peaks: dict) -> dict:
+    """Each kernel of the design alone beside the like kernel of the Llama path, as fractions of the measured copy
+    bandwidth (kernels that stream) or product throughput (attention over prompts); inputs larger than L2."""
+    import torch
+
+    from liteinfer_b200 import ops
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops_burst"] * 1e12
+    out: dict = {}
+
+    def ints(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def in_graph(fn, inner: int = 10) -> float:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, repeats=10, warmup=2) / inner
+
+    # -- the norm between two sublayers: four 32-bit streams of 16,384 x 2,048 rewritten, read and normalised
+    T, W, S = 16384, 2048, 4
+    x = torch.randn(T, S * W, device=dev)
+    y, normed = torch.randn(T, W, device=dev).to(bf), torch.empty(T, W, dtype=bf, device=dev)
+    weight, gain = torch.ones(W, device=dev), torch.ones(W, device=dev)
+    read, write, mix = torch.full((S,), 0.25, device=dev), torch.full((S,), 0.1, device=dev), torch.eye(S, device=dev)
+    ms = _timed(lambda: ops.stream_rmsnorm(x, weight, 1e-5, normed, read=read, update=ops.StreamUpdate(y, gain, write, mix)))
+    out["stream_rmsnorm_fused_hbm_frac"] = T * W * (8 * S + 2 + 2) / (ms * 1e-3) / hbm
+    out["stream_rmsnorm_fused_us"] = ms * 1e3
+    x16, w16 = torch.randn(T, W, device=dev).to(bf), torch.ones(W, dtype=bf, device=dev)
+    ms = _timed(lambda: ops.rmsnorm(x16, w16, 1e-5, normed, delta=y, write_residual=True))
+    out["llama_rmsnorm_fused_hbm_frac"] = T * W * (2 + 2 + 2 + 2) / (ms * 1e-3) / hbm
+
+    # -- the feed-forward's activation (16,384 x 8,192) beside the gated one
+    F = 8192
+    hidden, gate_up, act = torch.randn(T, F, device=dev).to(bf), torch.randn(T, 2 * F, device=dev).to(bf), torch.empty(T, F, dtype=bf, device=dev)
+    ms = _timed(lambda: ops.activation(hidden, act, "relu_squared"))
+    out["relu_squared_hbm_frac"] = T * F * 4 / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.act_mul(gate_up, act, "silu"))
+    out["llama_act_mul_hbm_frac"] = T * F * 6 / (ms * 1e-3) / hbm
+
+    # -- latent attention (16 heads, latent 512 + 64 rotated) beside grouped-query attention (16 / 4 heads of 128)
+    H, C, R, dm, page, n = 16, 512, 64, 128, 16, 2048
+    pages = n // page
+    inv_freq = (10000.0 ** (-torch.arange(R // 2, dtype=torch.float64) * 2 / R)).float().to(dev)
+    sink = torch.zeros(H, device=dev)
+    pool = (torch.randn(pages * 64, 1, page, C + R, device=dev) * 0.3).to(bf)
+    kv_heads, hd = 4, 128
+    k_pool = torch.randn(pages * 64, kv_heads, page, hd, device=dev).to(bf)
+    v_pool = torch.randn(pages * 64, kv_heads, page, hd, device=dev).to(bf)
+    # a prompt of 2,048
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    q_lat, q_raw = (torch.randn(H, n, C, device=dev) * 0.3).to(bf), torch.randn(n, H * (dm + R), device=dev).to(bf)
+    o_lat = torch.empty_like(q_lat)
+    plan = AttentionPlan(num_prefill=1, prefill_seqs=ints([0]), max_prefill_query_len=n)
+    ms = _timed(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, ints([0, n]), ints([n]), inv_freq,
+                                             sink, 1, n, H, C, R, R, 0.07, plan=plan))
+    out["latent_attention_prompt_us"] = ms * 1e3
+    out["latent_attention_prompt_tflops_frac"] = 2 * H * (2 * C + R) * n * (n + 1) / 2 / (ms * 1e-3) / tflops
+    q = torch.randn(n, H * hd, device=dev).to(bf)
+    o = torch.empty_like(q)
+    args = (q, q.shape[1], o, k_pool, v_pool, table, ints([0, n]), ints([n]), 1, n, H, kv_heads, hd, hd ** -0.5)
+    ms = _timed(lambda: ops.paged_attention(*args, 0, plan=plan))
+    out["llama_attention_prompt_us"] = ms * 1e3
+    out["llama_attention_prompt_tflops_frac"] = 4 * H * hd * n * (n + 1) / 2 / (ms * 1e-3) / tflops
+    # single tokens at batch 64 and 8 over 2,048 keys
+    for B in (64, 8):
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages)
+        q_lat, q_raw = (torch.randn(H, B, C, device=dev) * 0.3).to(bf), torch.randn(B, H * (dm + R), device=dev).to(bf)
+        o_lat = torch.empty_like(q_lat)
+        plan = AttentionPlan(num_decode=B, decode_seqs=ints(list(range(B))), decode_tokens=ints(list(range(B))),
+                             max_decode_context_len=n)
+        qsl, ctxl = ints(list(range(B + 1))), ints([n] * B)
+        ms = in_graph(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, qsl, ctxl, inv_freq, sink,
+                                                   B, 1, H, C, R, R, 0.07, plan=plan))
+        out[f"latent_attention_decode_b{B}_us"] = ms * 1e3
+        out[f"latent_attention_decode_b{B}_hbm_frac"] = B * n * (C + R) * 2 / (ms * 1e-3) / hbm
+        q = torch.randn(B, H * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        args = (q, q.shape[1], o, k_pool, v_pool, table, qsl, ctxl, B, 1, H, kv_heads, hd, hd ** -0.5)
+        ms = in_graph(lambda: ops.paged_attention(*args, 0, plan=plan))
+        out[f"llama_attention_decode_b{B}_us"] = ms * 1e3
+        out[f"llama_attention_decode_b{B}_hbm_frac"] = B * n * kv_heads * hd * 2 * 2 / (ms * 1e-3) / hbm
+    return {k: round(v, 4) for k, v in out.items()}
+
+
+def run_kegizen(args, which: str = "kegizen") -> dict:
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 near a context of 2,048) of a Kegizen (or
+    Gifudra) model and of a Llama model with the same width, depth, head sizes and feed-forward, random weights,
+    bfloat16; and the design's kernels one by one.  Printed as one JSON line; the default run of this file does not
+    include it."""
     import torch
 
     from liteinfer_b200 import LLM, SamplingParams
@@ -451,13 +557,17 @@ def run_kegizen(args) -> dict:
     greedy = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True)
     sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=32, kv_heads=8, head_dim=64),
              "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
-    result: dict = {"impl": "ours", "compare": "kegizen", "dtype": "bf16", "data": "synthetic ids, random weights",
+    if which == "gifudra":      # heads of 128 in both sizes: the latent attention's heads are 128 + 64 wide
+        sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=16, kv_heads=4, head_dim=128),
+                 "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
+    design = _gifudra_config if which == "gifudra" else _kegizen_config
+    result: dict = {"impl": "ours", "compare": which, "dtype": "bf16", "data": "synthetic ids, random weights",
                     "peaks": peaks, "models": {}}
     for name, size in sizes.items():
         llama = dict(LLAMA_1B, vocab_size=vocab, hidden_size=size["width"], intermediate_size=size["ff"],
                      num_hidden_layers=size["layers"], num_attention_heads=size["heads"],
                      num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"], tie_word_embeddings=False)
-        for arch, cfg in (("kegizen", _kegizen_config(vocab=vocab, **size)), ("llama", llama)):
+        for arch, cfg in ((which, design(vocab=vocab, **size)), ("llama", llama)):
             with tempfile.TemporaryDirectory() as tmp:
                 model_dir = write_random_model(cfg, Path(tmp) / arch, seed=0)
                 llm = LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=context + 1,
@@ -484,7 +594,7 @@ def run_kegizen(args) -> dict:
                 runner.check_kernels()
                 llm.close()
                 result["models"][f"{name}_{arch}"] = numbers
-    result["kernels"] = _kegizen_kernels(peaks)
+    result["kernels"] = _gifudra_kernels(peaks) if which == "gifudra" else _kegizen_kernels(peaks)
     return result
 
 
@@ -625,9 +735,9 @@ def main() -> int:
     parser.add_argument("--workload", default="none", choices=["none", "3b", "8b", "all"],
                         help="run the reference's larger configurations instead (64 requests under continuous batching "
                              "at the 3B sizes; decode at a context of 8,192 at the 8B sizes) and print their line")
-    parser.add_argument("--compare", default="none", choices=["none", "kegizen"],
-                        help="instead of the default run: the Kegizen decoder beside the Llama decoder at equal "
-                             "layer sizes (prefill, decode, and the design's kernels one by one)")
+    parser.add_argument("--compare", default="none", choices=["none", "kegizen", "gifudra"],
+                        help="instead of the default run: the Kegizen (or Gifudra) decoder beside the Llama decoder at "
+                             "equal layer sizes (prefill, decode, and the design's kernels one by one)")
     parser.add_argument("--no-workloads", action="store_true",
                         help="leave the 3B and 8B configurations out of the default run (they add about 80 s)")
     args = parser.parse_args()
@@ -635,8 +745,8 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print("liteinfer_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
         return 2
-    if args.compare == "kegizen" and args.impl == "ours":
-        print(json.dumps(run_kegizen(args)))
+    if args.compare != "none" and args.impl == "ours":
+        print(json.dumps(run_kegizen(args, args.compare)))
         return 0
     if args.workload != "none" and args.impl == "ours":
         print(json.dumps({"impl": "ours", "workloads": run_workloads(args)}))

@@ -1,0 +1,437 @@
+// Latent attention on tensor cores (bfloat16): multi-query attention of up to 16 heads per row tile over the
+// shared cache entries [latent (C) | rotated key part (R)], whose first C numbers are also the values
+// (attention_latent.cu has the formulas and the SIMT kernel for every other size and for float32).
+//
+// A block of eight warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
+// the keys KT at a time (cp.async into padded shared memory, two stages, the next tile on its way while this
+// one is used).  Per tile of keys:
+//   1. scores: the MT x (KT / 8) units of 16 rows x 8 keys are dealt to the warps; a unit is (C + R) / 16
+//      mma.sync m16n8k16 with the query rows (shared memory, ldmatrix) and the keys as they are stored
+//      ([key][number] is the product's column-major operand).  Scale, causal mask, the unit's row maxima.
+//   2. every row's new maximum from the units' maxima; probabilities, rounded to bfloat16, into shared memory;
+//      the units' row sums.
+//   3. values: warp w owns numbers [w * C / 8, (w + 1) * C / 8) of every row's accumulator (registers), rescales
+//      them when a maximum moved and adds P V with the stored entries as the row-major operand (ldmatrix.trans).
+// Three block barriers per tile.  Maxima are kept twice (the tile's old and new one) so that step 3 still finds the
+// old one; sums are kept by the rows' own threads.  At the end the sink's term joins the denominator.
+//
+// Launches: sequences that bring one token run with MT = 1 and KT = 64 (16 rows of 16 heads stream a sequence's
+// entries once), their keys split over `num_splits` blocks whose partial results (normalised, with the logarithm
+// of their denominators) a second kernel merges, sink included.  Sequences that bring more run with MT = 4 and
+// KT = 32: four consecutive queries share every tile of keys.
+#include "attention_mma.cuh"
+
+namespace li {
+
+struct LatentParams {
+  const bf16* q_lat; long q_lat_head_stride; int q_lat_token_stride;
+  const bf16* q_raw; int q_raw_token_stride, q_raw_head_stride, q_rot_off;
+  bf16* out; long out_head_stride; int out_token_stride;
+  const bf16* pool;
+  const int* block_table; int table_stride;
+  const int* query_start_loc; const int* context_lens;
+  const int* seq_index;         // optional: batch row of each launched sequence (-1: a place of padding)
+  const float* inv_freq; const float* sink;
+  int heads, rot_dims, page_size, num_pages;
+  float scale_log2;             // scale * log2(e)
+  int num_splits;
+  float* partial_out;           // [splits][heads][tokens][C] when num_splits > 1
+  float* partial_lse;           // [splits][heads][tokens], in units of log2
+  int tokens;
+};
+
+constexpr int kLatentWarps = 8;
+constexpr int kPad = 8;         // bfloat16 of padding per shared-memory row: rows 16 bytes apart modulo 128
+
+template <int C, int R, int MT, int KT>
+struct LatentSmem {
+  static constexpr int D = C + R, LD = D + kPad, PLD = KT + kPad;
+  static constexpr int kRows = MT * 16, kUnits = MT * (KT / 8);
+  static constexpr size_t q_bytes = (size_t)kRows * LD * 2;
+  static constexpr size_t k_bytes = (size_t)KT * LD * 2;
+  static constexpr size_t p_bytes = (size_t)kRows * PLD * 2;
+  static constexpr size_t f_floats = (size_t)kRows * (KT / 8) * 2 + kRows * 4;
+  static constexpr size_t total = q_bytes + 2 * k_bytes + p_bytes + f_floats * 4;
+};
+
+template <int C, int R, int KT>
+__device__ __forceinline__ void load_key_tile(bf16* ks, const LatentParams& p, const int* table, int key0, int limit) {
+  constexpr int D = C + R, LD = D + kPad, kChunks = D / 8;
+  for (int i = threadIdx.x; i < KT * kChunks; i += kLatentWarps * 32) {
+    const int key = i / kChunks, chunk = i - key * kChunks;
+    const int kpos = key0 + key;
+    bool valid = kpos < limit;
+    size_t off = 0;
+    if (valid) {
+      const int page = table[kpos / p.page_size];
+      valid = page >= 0 && page < p.num_pages;
+      if (valid) off = ((size_t)page * p.page_size + kpos % p.page_size) * D + chunk * 8;
+    }
+    cp_async16(ks + key * LD + chunk * 8, p.pool + off, valid);      // an entry that is not visible arrives as zeros
+  }
+}
+
+template <int C, int R, int MT, int KT>
+__global__ void __launch_bounds__(kLatentWarps * 32, 1)
+latent_attention_mma_kernel(const LatentParams p) {
+  using S = LatentSmem<C, R, MT, KT>;
+  constexpr int D = S::D, LD = S::LD, PLD = S::PLD, kRows = S::kRows, kNTiles = KT / 8;
+  constexpr int kOwn = C / kLatentWarps;         // numbers of the accumulator a warp owns
+  constexpr int kOwnTiles = kOwn / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);
+  bf16* ks0 = reinterpret_cast<bf16*>(smem_raw + S::q_bytes);
+  bf16* ps = reinterpret_cast<bf16*>(smem_raw + S::q_bytes + 2 * S::k_bytes);
+  float* unit_max = reinterpret_cast<float*>(smem_raw + S::q_bytes + 2 * S::k_bytes + S::p_bytes);   // [kNTiles][kRows]
+  float* unit_sum = unit_max + kNTiles * kRows;                                                       // [kNTiles][kRows]
+  float* row_max = unit_sum + kNTiles * kRows;                                                        // [2][kRows]
+  float* row_sum = row_max + 2 * kRows;                                                               // [kRows]
+  float* row_inv = row_sum + kRows;                                                                   // [kRows]
+
+  grid_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int split = p.num_splits > 1 ? blockIdx.x % p.num_splits : 0;
+  const int tile_index = p.num_splits > 1 ? blockIdx.x / p.num_splits : blockIdx.x;
+  const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  if (seq < 0) return;
+  const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
+  const int query0 = tile_index * MT;
+  if (query0 >= q_len) return;
+  const int ctx = p.context_lens[seq];
+  const int head0 = blockIdx.y * 16;
+  const int* table = p.block_table + (size_t)seq * p.table_stride;
+  const int first_pos = ctx - q_len + query0;                        // position of the block's first query
+  const int last_pos = min(first_pos + MT - 1, ctx - 1);             // of its last one: the keys end there
+  const int all_tiles = last_pos / KT + 1;
+  const int per_split = (all_tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = split * per_split, tile_end = min(all_tiles, tile_begin + per_split);
+
+  grid_dependency_wait();      // the entries of this step's tokens and the queries come from kernels ahead
+  if (tile_begin < tile_end) load_key_tile<C, R, KT>(ks0, p, table, tile_begin * KT, last_pos + 1);
+  cp_async_commit();
+
+  // The query rows: row 16 * i + j is head head0 + j of query query0 + i; [absorbed query | rotated part].
+  for (int i = threadIdx.x; i < kRows * (C / 8); i += kLatentWarps * 32) {
+    const int row = i / (C / 8), chunk = i - row * (C / 8);
+    const int query = query0 + row / 16, head = head0 + row % 16;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (query < q_len && head < p.heads)
+      v = *reinterpret_cast<const uint4*>(p.q_lat + (size_t)head * p.q_lat_head_stride +
+                                          (size_t)(q_begin + query) * p.q_lat_token_stride + chunk * 8);
+    *reinterpret_cast<uint4*>(qs + row * LD + chunk * 8) = v;
+  }
+  {
+    const int half = p.rot_dims / 2;
+    for (int i = threadIdx.x; i < kRows * R; i += kLatentWarps * 32) {
+      const int row = i / R, d = i - row * R;
+      const int query = query0 + row / 16, head = head0 + row % 16;
+      float v = 0.f;
+      if (query < q_len && head < p.heads) {
+        const bf16* qr = p.q_raw + (size_t)(q_begin + query) * p.q_raw_token_stride + (size_t)head * p.q_raw_head_stride + p.q_rot_off;
+        if (d < p.rot_dims) {
+          const int j = d < half ? d : d - half;
+          const float angle = __fmul_rn((float)(first_pos + row / 16), p.inv_freq[j]);
+          const float c = cosf(angle), s = sinf(angle);
+          const float a = to_float(qr[j]), b = to_float(qr[j + half]);
+          v = d < half ? rotate_lo(a, b, c, s) : rotate_hi(a, b, c, s);
+        } else {
+          v = to_float(qr[d]);
+        }
+      }
+      qs[row * LD + C + d] = __float2bfloat16_rn(v);
+    }
+  }
+  for (int i = threadIdx.x; i < kRows; i += kLatentWarps * 32) {
+    row_max[i] = -INFINITY;
+    row_max[kRows + i] = -INFINITY;
+    row_sum[i] = 0.f;
+  }
+
+  float acc[MT][kOwnTiles][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int n = 0; n < kOwnTiles; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][n][e] = 0.f;
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int it = tile - tile_begin;
+    bf16* ks = ks0 + (size_t)(it & 1) * KT * LD;
+    bf16* ks_next = ks0 + (size_t)((it + 1) & 1) * KT * LD;
+    if (tile + 1 < tile_end) load_key_tile<C, R, KT>(ks_next, p, table, (tile + 1) * KT, last_pos + 1);
+    cp_async_commit();
+    cp_async_wait<1>();           // this tile's entries have landed (the next one's may be on their way)
+    __syncthreads();
+    const float* old_max = row_max + (it & 1) * kRows;
+    float* new_max = row_max + ((it + 1) & 1) * kRows;
+    const int key0 = tile * KT;
+
+    // 1. scores of this warp's units, kept in registers: unit u = (row tile u / kNTiles, keys 8 * (u % kNTiles)...).
+    constexpr int kUnitsPerWarp = (S::kUnits + kLatentWarps - 1) / kLatentWarps;
+    float sc[kUnitsPerWarp][4];
+#pragma unroll
+    for (int uu = 0; uu < kUnitsPerWarp; ++uu) {
+      const int u = warp + uu * kLatentWarps;
+      sc[uu][0] = sc[uu][1] = sc[uu][2] = sc[uu][3] = 0.f;
+      if (u >= S::kUnits) continue;
+      const int mt = u / kNTiles, nt = u % kNTiles;
+      const bf16* qa = qs + (mt * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
+      const bf16* kb = ks + (nt * 8 + (lane & 7)) * LD + (lane >> 3) * 8;
+#pragma unroll 4
+      for (int k0 = 0; k0 < D; k0 += 32) {
+        unsigned a[4], a2[4], b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, kb + k0);          // keys nt*8.., numbers k0..k0+31: two k-steps
+        ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
+        mma_bf16(sc[uu], a, b0, b1);
+        if (k0 + 16 < D) {
+          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
+          mma_bf16(sc[uu], a2, b2, b3);
+        }
+      }
+      // Scale, mask (key j is visible to the query at position pos iff j <= pos), and the unit's row maxima.
+      const int pos = first_pos + mt;
+      const int kcol = key0 + nt * 8 + 2 * t4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kcol + (e & 1);
+        sc[uu][e] = key <= pos ? sc[uu][e] * p.scale_log2 : -INFINITY;
+      }
+      float m_lo = fmaxf(sc[uu][0], sc[uu][1]), m_hi = fmaxf(sc[uu][2], sc[uu][3]);
+      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
+      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
+      if (t4 == 0) {
+        unit_max[nt * kRows + mt * 16 + g] = m_lo;
+        unit_max[nt * kRows + mt * 16 + g + 8] = m_hi;
+      }
+    }
+    __syncthreads();
+
+    // 2. the rows' new maxima (their own threads store them), probabilities into shared memory, the units' sums.
+    if (threadIdx.x < kRows) {
+      float m = old_max[threadIdx.x];
+#pragma unroll
+      for (int n = 0; n < kNTiles; ++n) m = fmaxf(m, unit_max[n * kRows + threadIdx.x]);
+      new_max[threadIdx.x] = m;
+    }
+#pragma unroll
+    for (int uu = 0; uu < kUnitsPerWarp; ++uu) {
+      const int u = warp + uu * kLatentWarps;
+      if (u >= S::kUnits) continue;
+      const int mt = u / kNTiles, nt = u % kNTiles;
+      const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+      float m_lo = old_max[r_lo], m_hi = old_max[r_hi];
+#pragma unroll
+      for (int n = 0; n < kNTiles; ++n) {
+        m_lo = fmaxf(m_lo, unit_max[n * kRows + r_lo]);
+        m_hi = fmaxf(m_hi, unit_max[n * kRows + r_hi]);
+      }
+      const float p0 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[uu][0] - m_lo);
+      const float p1 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[uu][1] - m_lo);
+      const float p2 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[uu][2] - m_hi);
+      const float p3 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[uu][3] - m_hi);
+      *reinterpret_cast<__nv_bfloat162*>(ps + r_lo * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p0, p1);
+      *reinterpret_cast<__nv_bfloat162*>(ps + r_hi * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p2, p3);
+      float s_lo = p0 + p1, s_hi = p2 + p3;
+      s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1);
+      s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+      s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1);
+      s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+      if (t4 == 0) {
+        unit_sum[nt * kRows + r_lo] = s_lo;
+        unit_sum[nt * kRows + r_hi] = s_hi;
+      }
+    }
+    __syncthreads();
+
+    // 3. the rows' sums (their own threads), and every warp's share of the accumulators.
+    if (threadIdx.x < kRows) {
+      const float m_old = old_max[threadIdx.x], m_new = new_max[threadIdx.x];
+      float s = 0.f;
+#pragma unroll
+      for (int n = 0; n < kNTiles; ++n) s += unit_sum[n * kRows + threadIdx.x];
+      const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_old - m_new);
+      row_sum[threadIdx.x] = row_sum[threadIdx.x] * alpha + s;
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+      const float n_lo = new_max[r_lo], n_hi = new_max[r_hi];
+      const float a_lo = n_lo == -INFINITY ? 1.f : fast_exp2(old_max[r_lo] - n_lo);
+      const float a_hi = n_hi == -INFINITY ? 1.f : fast_exp2(old_max[r_hi] - n_hi);
+      if (a_lo != 1.f || a_hi != 1.f) {
+#pragma unroll
+        for (int n = 0; n < kOwnTiles; ++n) {
+          acc[mt][n][0] *= a_lo; acc[mt][n][1] *= a_lo;
+          acc[mt][n][2] *= a_hi; acc[mt][n][3] *= a_hi;
+        }
+      }
+      const bf16* pa = ps + (mt * 16 + (lane & 15)) * PLD + (lane >> 4) * 8;
+#pragma unroll
+      for (int k0 = 0; k0 < KT; k0 += 16) {
+        unsigned a[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], pa + k0);
+        const bf16* vb = ks + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + warp * kOwn + (lane >> 4) * 8;
+#pragma unroll
+        for (int n = 0; n < kOwnTiles; n += 2) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vb + n * 8);      // keys k0..k0+15, numbers of two 8-wide tiles
+          mma_bf16(acc[mt][n], a, b0, b1);
+          if (n + 1 < kOwnTiles) mma_bf16(acc[mt][n + 1], a, b2, b3);
+        }
+      }
+    }
+    __syncthreads();      // the probabilities and this stage of entries may be overwritten
+  }
+  cp_async_wait<0>();
+
+  // The end: denominators (with the sink's term where this block sees all keys), then the rows leave.
+  const int final_buf = ((tile_end > tile_begin ? tile_end - tile_begin : 0) & 1) * kRows;
+  if (threadIdx.x < kRows) {
+    const int head = head0 + threadIdx.x % 16;
+    float m = row_max[final_buf + threadIdx.x], l = row_sum[threadIdx.x];
+    if (p.num_splits <= 1) {
+      if (p.sink && head < p.heads) {
+        const float sk = p.sink[head] * kLog2e;
+        const float m_new = fmaxf(m, sk);
+        const float alpha = m == -INFINITY ? 0.f : fast_exp2(m - m_new);
+        l = l * alpha + fast_exp2(sk - m_new);
+        row_inv[threadIdx.x] = l > 0.f ? alpha / l : 0.f;
+      } else {
+        row_inv[threadIdx.x] = l > 0.f ? 1.f / l : 0.f;
+      }
+    } else {
+      row_inv[threadIdx.x] = l > 0.f ? 1.f / l : 0.f;
+      const int query = query0 + threadIdx.x / 16;
+      if (query < q_len && head < p.heads)
+        p.partial_lse[((size_t)split * p.heads + head) * p.tokens + q_begin + query] = l > 0.f ? m + log2f(l) : -INFINITY;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    const int query = query0 + mt;
+    if (query >= q_len) continue;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int head = head0 + g + hh * 8;
+      if (head >= p.heads) continue;
+      const float inv = row_inv[mt * 16 + g + hh * 8];
+#pragma unroll
+      for (int n = 0; n < kOwnTiles; ++n) {
+        const int col = warp * kOwn + n * 8 + 2 * t4;
+        const float x = acc[mt][n][2 * hh] * inv, y = acc[mt][n][2 * hh + 1] * inv;
+        if (p.num_splits <= 1) {
+          bf16* o = p.out + (size_t)head * p.out_head_stride + (size_t)(q_begin + query) * p.out_token_stride + col;
+          *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(x, y);
+        } else {
+          float* o = p.partial_out + (((size_t)split * p.heads + head) * p.tokens + q_begin + query) * C + col;
+          *reinterpret_cast<float2*>(o) = make_float2(x, y);
+        }
+      }
+    }
+  }
+}
+
+// The splits of a (token, head) row merged: out = sum_s w_s O_s / (sum_s w_s + the sink's term), w_s = 2^(lse_s - max).
+__global__ void latent_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
+                                    const int* __restrict__ seq_index, const int* __restrict__ query_start_loc,
+                                    bf16* __restrict__ out, long out_head_stride,
+                                    int out_token_stride, const float* __restrict__ sink, int heads, int tokens,
+                                    int C, int num_splits) {
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const int seq = seq_index ? seq_index[blockIdx.x] : blockIdx.x;
+  const int head = blockIdx.y;
+  if (seq < 0) return;                            // a place of padding
+  const int token = query_start_loc[seq];         // the sequence's one token
+  float m = sink ? sink[head] * kLog2e : -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, partial_lse[((size_t)s * heads + head) * tokens + token]);
+  float denom = sink ? exp2f(sink[head] * kLog2e - m) : 0.f;
+  for (int s = 0; s < num_splits; ++s) denom += exp2f(partial_lse[((size_t)s * heads + head) * tokens + token] - m);
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int d = threadIdx.x; d < C; d += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const size_t row = ((size_t)s * heads + head) * tokens + token;
+      const float w = exp2f(partial_lse[row] - m);
+      if (w > 0.f) v = fmaf(w, partial_out[row * C + d], v);
+    }
+    out[(size_t)head * out_head_stride + (size_t)token * out_token_stride + d] = __float2bfloat16_rn(v * inv);
+  }
+}
+
+template <int C, int R, int MT, int KT>
+int launch_latent(const LatentParams& p, int num_seqs, int row_tiles, cudaStream_t stream) {
+  using S = LatentSmem<C, R, MT, KT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::total);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const dim3 grid(row_tiles * (p.num_splits > 1 ? p.num_splits : 1), (p.heads + 15) / 16, num_seqs);
+  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT>, grid, dim3(kLatentWarps * 32),
+                         S::total, stream, p);
+}
+
+template <int C, int R>
+int launch_latent_sizes(const LatentParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
+  if (max_q_len == 1) return launch_latent<C, R, 1, 64>(p, num_seqs, 1, stream);
+  return launch_latent<C, R, 4, 32>(p, num_seqs, (max_q_len + 3) / 4, stream);
+}
+
+}  // namespace li
+
+using namespace li;
+
+LI_EXPORT int li_latent_attention_mma_supports(int kv_rank, int rot_dim, int rot_dims) {
+  const bool sizes = (kv_rank == 64 && rot_dim == 32) || (kv_rank == 128 && (rot_dim == 32 || rot_dim == 64)) ||
+                     (kv_rank == 256 && rot_dim == 64) || (kv_rank == 512 && rot_dim == 64);
+  return sizes && rot_dims >= 0 && rot_dims <= rot_dim && (rot_dims & 1) == 0;
+}
+
+// As li_latent_attention (attention_latent.cu), bfloat16 only, for the sizes `..._supports` names.  seq_index
+// [num_seqs] or null: the batch rows to run (-1: none); max_q_len 1 runs the single-token form, whose keys
+// `num_splits` blocks share (partial_out [splits, heads, tokens, kv_rank] and partial_lse [splits, heads, tokens]
+// float; `tokens`: the step's token rows).
+LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
+                                      const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
+                                      void* out, long out_head_stride, int out_token_stride, const void* pool,
+                                      const int* block_table, int table_stride, const int* query_start_loc,
+                                      const int* context_lens, const int* seq_index, const float* inv_freq,
+                                      const float* sink, int num_seqs, int max_q_len, int heads, int kv_rank,
+                                      int rot_dim, int rot_dims, int page_size, int num_pages, float scale,
+                                      int num_splits, float* partial_out, float* partial_lse, int tokens,
+                                      cudaStream_t stream) {
+  if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (!li_latent_attention_mma_supports(kv_rank, rot_dim, rot_dims) || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
+  if (!aligned16(q_lat) || !aligned16(pool) || (q_lat_token_stride % 8) || (q_lat_head_stride % 8) || (out_token_stride % 2) ||
+      (out_head_stride % 2))
+    return LI_ERR_ALIGNMENT;
+  if (max_q_len != 1) num_splits = 1;
+  if (num_splits > 1 && (!partial_out || !partial_lse)) return LI_ERR_UNSUPPORTED;
+  LatentParams p;
+  p.q_lat = (const bf16*)q_lat; p.q_lat_head_stride = q_lat_head_stride; p.q_lat_token_stride = q_lat_token_stride;
+  p.q_raw = (const bf16*)q_raw; p.q_raw_token_stride = q_raw_token_stride; p.q_raw_head_stride = q_raw_head_stride;
+  p.q_rot_off = q_rot_off;
+  p.out = (bf16*)out; p.out_head_stride = out_head_stride; p.out_token_stride = out_token_stride;
+  p.pool = (const bf16*)pool; p.block_table = block_table; p.table_stride = table_stride;
+  p.query_start_loc = query_start_loc; p.context_lens = context_lens; p.seq_index = seq_index;
+  p.inv_freq = inv_freq; p.sink = sink; p.heads = heads; p.rot_dims = rot_dims; p.page_size = page_size;
+  p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.num_splits = num_splits < 1 ? 1 : num_splits;
+  p.partial_out = partial_out; p.partial_lse = partial_lse; p.tokens = tokens;
+  int code;
+  if (kv_rank == 64) code = launch_latent_sizes<64, 32>(p, num_seqs, max_q_len, stream);
+  else if (kv_rank == 128 && rot_dim == 32) code = launch_latent_sizes<128, 32>(p, num_seqs, max_q_len, stream);
+  else if (kv_rank == 128) code = launch_latent_sizes<128, 64>(p, num_seqs, max_q_len, stream);
+  else if (kv_rank == 256) code = launch_latent_sizes<256, 64>(p, num_seqs, max_q_len, stream);
+  else code = launch_latent_sizes<512, 64>(p, num_seqs, max_q_len, stream);
+  if (code != 0 || p.num_splits <= 1) return code;
+  return (int)launch_pdl(num_seqs, latent_merge_kernel, dim3(num_seqs, heads), dim3(128), 0, stream,
+                         (const float*)partial_out, (const float*)partial_lse, seq_index, query_start_loc, (bf16*)out,
+                         out_head_stride, out_token_stride, sink, heads, tokens, kv_rank, p.num_splits);
+}

@@ -105,6 +105,11 @@ _SIGNATURES = {
                                                  c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                  c_int, c_float, c_void_p]),
+    "li_latent_attention_mma": ("attention_latent_mma", [
+        c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "li_latent_attention_mma_supports": ("attention_latent_mma", [c_int, c_int, c_int]),
     "li_gate_heads": ("attention_latent", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p]),
@@ -1208,6 +1213,33 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
     assert q_lat.dtype == q_raw.dtype == out.dtype == pool.dtype
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads)
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dims
+    if latent_mma_supports(q_raw.dtype, kv_rank, rot_dim, rot_dims):
+        # Tensor cores: sequences that bring one token in a launch that splits their keys over blocks, the others
+        # four queries a block; without a plan every sequence goes the second way.
+        def run(seq_index, count, q_len, splits=1):
+            partial_out = partial_lse = None
+            if splits > 1:
+                partial_out = torch.empty((splits, heads, tokens, kv_rank), dtype=torch.float32, device=out.device)
+                partial_lse = torch.empty((splits, heads, tokens), dtype=torch.float32, device=out.device)
+            _check(_fn("li_latent_attention_mma")(
+                q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_raw.data_ptr(), q_raw.stride(0), q_head_stride,
+                q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
+                block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), _ptr(seq_index),
+                inv_freq.data_ptr(), _ptr(sink), count, q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages,
+                float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens, _stream()),
+                "latent_attention_mma")
+
+        if plan is None:
+            run(None, num_seqs, max(max_q_len, 2))
+            return out
+        if plan.num_prefill:
+            run(plan.prefill_seqs, plan.num_prefill, max(plan.max_prefill_query_len, 2))
+        if plan.num_decode:
+            chunks = -(-heads // 16)
+            tiles = max(1, -(-plan.max_decode_context_len // 64))
+            splits = max(1, min(tiles, (2 * NUM_SMS) // max(1, plan.num_decode * chunks), 32))
+            run(plan.decode_seqs, plan.num_decode, 1, splits)
+        return out
     _check(_fn("li_latent_attention")(
         _code(q_raw), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_raw.data_ptr(), q_raw.stride(0),
         q_head_stride, q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
@@ -1215,6 +1247,13 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
         num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages, float(scale), _stream()),
         "latent_attention")
     return out
+
+
+def latent_mma_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int, rot_dims: int) -> bool:
+    """Whether the tensor-core latent attention takes these sizes (bfloat16; LITEINFER_LATENT_MMA=0 keeps every
+    size on the SIMT kernel)."""
+    return (dtype == torch.bfloat16 and os.environ.get("LITEINFER_LATENT_MMA", "1") != "0"
+            and bool(_fn("li_latent_attention_mma_supports")(kv_rank, rot_dim, rot_dims)))
 
 
 def gate_heads(v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:

@@ -202,17 +202,54 @@ def test_latent_attention_portions_and_single_tokens(dtype, heads, c, r, dims, d
     torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+def _plan(query_lens, context_lens):
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    decode = [i for i, n in enumerate(query_lens) if n == 1]
+    prefill = [i for i, n in enumerate(query_lens) if n > 1]
+    starts = [sum(query_lens[:i]) for i in range(len(query_lens))]
+    return AttentionPlan(num_decode=len(decode) + 1, decode_seqs=_ints(decode + [-1]),          # one place of padding each
+                         decode_tokens=_ints([starts[i] for i in decode] + [0]), num_prefill=len(prefill) + 1,
+                         prefill_seqs=_ints(prefill + [-1]), max_prefill_query_len=max([query_lens[i] for i in prefill], default=0),
+                         max_decode_context_len=max([context_lens[i] for i in decode], default=0))
+
+
+@pytest.mark.parametrize("heads,c,r,page", [(16, 64, 32, 16), (8, 128, 32, 32), (20, 128, 64, 16), (5, 256, 64, 64),
+                                            (16, 512, 64, 16), (33, 512, 64, 32)])
+@pytest.mark.parametrize("sink", [True, False])
+def test_latent_attention_on_tensor_cores_with_a_plan(heads, c, r, page, sink):
+    """Sizes the tensor-core kernel takes: portions (four queries a block) beside single tokens whose keys several
+    blocks share, places of padding in both lists, against the plain twin and against the SIMT kernel."""
+    from liteinfer_b200 import ops
+
+    dtype, d = torch.bfloat16, 8
+    assert ops.latent_mma_supports(dtype, c, r, r)
+    query_lens, context_lens = [1, 37, 1, 6, 1, 130], [900, 37, 1, 70, 65, 130 + 2 * page + 3]
+    pages = sum(-(-n // page) for n in context_lens) + 3
+    table, qsl, ctxl, pool, q_lat, q_raw = _attention_inputs(dtype, heads, c, r, d, query_lens, context_lens, page, pages, 7)
+    inv_freq = (1000.0 ** (-torch.arange(r // 2, dtype=torch.float64) * 2 / r)).float().to(DEV)
+    sinks = _randn(heads, seed=9) if sink else None
+    common = (q_lat, q_raw, d + r, d)
+    rest = (pool, table, qsl, ctxl, inv_freq, sinks, 6, 130, heads, c, r, r, 0.09)
+    want = ref.latent_attention(*common, torch.empty_like(q_lat), *rest)
+    planned = ops.latent_attention(*common, torch.zeros_like(q_lat), *rest, plan=_plan(query_lens, context_lens))
+    unplanned = ops.latent_attention(*common, torch.zeros_like(q_lat), *rest)
+    torch.testing.assert_close(planned.float(), want.float(), **_tol(dtype))
+    torch.testing.assert_close(unplanned.float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype,c,r", [(torch.float32, 48, 8), (torch.bfloat16, 48, 8), (torch.bfloat16, 64, 32)])
 @pytest.mark.parametrize("decode", [False, True])
-def test_latent_attention_one_key_stands_out(dtype, decode):
+def test_latent_attention_one_key_stands_out(dtype, c, r, decode):
     """One key's score is lifted far above all others, wherever it lies: at position 0, on both sides of page
     borders, hundreds of tokens back, the query's own position.  The query then reads that entry's latent.  A key
     just behind the query's position is never seen, whatever it holds; a sink as large as the lifted score halves
     the result."""
     from liteinfer_b200 import ops
 
-    heads, c, r, d, page, ctx = 3, 48, 8, 6, 16, 700
+    heads, d, page, ctx = 3, 6, 16, 700
     n = 1 if decode else 9
+    plan = _plan([n], [ctx]) if c == 64 else None          # the tensor-core kernel: split keys for the single token
     pages = -(-ctx // page) + 2
     inv_freq = (1000.0 ** (-torch.arange(r // 2, dtype=torch.float64) * 2 / r)).float().to(DEV)
     qpos = ctx - 1
@@ -231,14 +268,14 @@ def test_latent_attention_one_key_stands_out(dtype, decode):
         q_lat[:, -1] = (lifted[:c] * 3.0).to(dtype)                   # the last query looks for exactly that latent
         sink = torch.full((heads,), -50.0, device=DEV)
         out = ops.latent_attention(q_lat, q_raw, d + r, d, torch.empty_like(q_lat), pool, table, qsl, ctxl, inv_freq,
-                                   sink, 1, n, heads, c, r, r, 1.0)
+                                   sink, 1, n, heads, c, r, r, 1.0, plan=plan)
         found = pool[entry_page, 0, slot, :c].float()
         if target <= qpos:
             torch.testing.assert_close(out[:, -1].float(), found.expand(heads, c), rtol=2e-2, atol=2e-2)
             score = float((q_lat[0, -1].float() * found).sum())
             sink = torch.full((heads,), score, device=DEV)
             halved = ops.latent_attention(q_lat, q_raw, d + r, d, torch.empty_like(q_lat), pool, table, qsl, ctxl,
-                                          inv_freq, sink, 1, n, heads, c, r, r, 1.0)
+                                          inv_freq, sink, 1, n, heads, c, r, r, 1.0, plan=plan)
             torch.testing.assert_close(halved[:, -1].float(), 0.5 * found.expand(heads, c), rtol=3e-2, atol=3e-2)
         else:
             assert float(out[:, -1].float().abs().max()) < 0.2      # an average of small entries: the lifted one is not in it
