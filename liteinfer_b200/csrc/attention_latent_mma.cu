@@ -56,18 +56,22 @@ struct LatentSmem {
 
 template <int C, int R, int KT>
 __device__ __forceinline__ void load_key_tile(bf16* ks, const LatentParams& p, const int* table, int key0, int limit) {
+  // A warp takes every eighth key: one look at the block table per key, then the lanes fetch the entry's 16-byte
+  // chunks in turn.  An entry that is not visible (behind the last query, or on a page given back) arrives as zeros.
   constexpr int D = C + R, LD = D + kPad, kChunks = D / 8;
-  for (int i = threadIdx.x; i < KT * kChunks; i += kLatentWarps * 32) {
-    const int key = i / kChunks, chunk = i - key * kChunks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int key = warp; key < KT; key += kLatentWarps) {
     const int kpos = key0 + key;
     bool valid = kpos < limit;
-    size_t off = 0;
+    const bf16* src = p.pool;
     if (valid) {
       const int page = table[kpos / p.page_size];
       valid = page >= 0 && page < p.num_pages;
-      if (valid) off = ((size_t)page * p.page_size + kpos % p.page_size) * D + chunk * 8;
+      if (valid) src = p.pool + ((size_t)page * p.page_size + kpos % p.page_size) * D;
     }
-    cp_async16(ks + key * LD + chunk * 8, p.pool + off, valid);      // an entry that is not visible arrives as zeros
+    bf16* dst = ks + key * LD;
+#pragma unroll
+    for (int chunk = lane; chunk < kChunks; chunk += 32) cp_async16(dst + chunk * 8, src + (valid ? chunk * 8 : 0), valid);
   }
 }
 
@@ -178,17 +182,27 @@ latent_attention_mma_kernel(const LatentParams p) {
       const int mt = u / kNTiles, nt = u % kNTiles;
       const bf16* qa = qs + (mt * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
       const bf16* kb = ks + (nt * 8 + (lane & 7)) * LD + (lane >> 3) * 8;
-#pragma unroll 4
-      for (int k0 = 0; k0 < D; k0 += 32) {
+      // Four partial sums, each over every fourth k-step: the products of one sum wait for each other, not for
+      // the other three's.
+      float part[3][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 3
+      for (int k0 = 0; k0 < D; k0 += 64) {
         unsigned a[4], a2[4], b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3, kb + k0);          // keys nt*8.., numbers k0..k0+31: two k-steps
         ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
+        ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
         mma_bf16(sc[uu], a, b0, b1);
-        if (k0 + 16 < D) {
-          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
-          mma_bf16(sc[uu], a2, b2, b3);
+        mma_bf16(part[0], a2, b2, b3);
+        if (k0 + 32 < D) {
+          ldmatrix_x4(b0, b1, b2, b3, kb + k0 + 32);
+          ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0 + 32);
+          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 48);
+          mma_bf16(part[1], a, b0, b1);
+          mma_bf16(part[2], a2, b2, b3);
         }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[uu][e] += part[0][e] + part[1][e] + part[2][e];
       // Scale, mask (key j is visible to the query at position pos iff j <= pos), and the unit's row maxima.
       const int pos = first_pos + mt;
       const int kcol = key0 + nt * 8 + 2 * t4;

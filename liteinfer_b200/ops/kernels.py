@@ -1237,7 +1237,9 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
         if plan.num_decode:
             chunks = -(-heads // 16)
             tiles = max(1, -(-plan.max_decode_context_len // 64))
-            splits = max(1, min(tiles, (2 * NUM_SMS) // max(1, plan.num_decode * chunks), 32))
+            # One block per SM (a block's two stages of entries fill most of its shared memory): as many splits
+            # as still make one wave.
+            splits = max(1, min(tiles, NUM_SMS // max(1, plan.num_decode * chunks), 32))
             run(plan.decode_seqs, plan.num_decode, 1, splits)
         return out
     _check(_fn("li_latent_attention")(
