@@ -2,24 +2,28 @@
 // shared cache entries [latent (C) | rotated key part (R)], whose first C numbers are also the values
 // (attention_latent.cu has the formulas and the SIMT kernel for every other size and for float32).
 //
-// A block of eight warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
-// the keys KT at a time (cp.async into padded shared memory, two stages, the next tile on its way while this
-// one is used).  Per tile of keys:
-//   1. scores: the MT x (KT / 8) units of 16 rows x 8 keys are dealt to the warps; a unit is (C + R) / 16
-//      mma.sync m16n8k16 with the query rows (shared memory, ldmatrix) and the keys as they are stored
+// A block of sixteen warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
+// the keys KT at a time (one bulk copy per entry into padded shared memory, a ring of stages behind mbarriers, the next
+// tiles on their way while this one is used).  Per tile of keys:
+//   1. scores: the MT x (KT / 8) units of 16 rows x 8 keys are dealt to the warps, one unit a warp, or two warps a
+//      unit, each then with a part of the (C + R) / 16 products and the halves added through shared memory; a
+//      product is mma.sync m16n8k16 with the query rows (shared memory, ldmatrix) and the keys as they are stored
 //      ([key][number] is the product's column-major operand).  Scale, causal mask, the unit's row maxima.
 //   2. every row's new maximum from the units' maxima; probabilities, rounded to bfloat16, into shared memory;
 //      the units' row sums.
-//   3. values: warp w owns numbers [w * C / 8, (w + 1) * C / 8) of every row's accumulator (registers), rescales
+//   3. values: warp w owns numbers [w * C / 16, (w + 1) * C / 16) of every row's accumulator (registers), rescales
 //      them when a maximum moved and adds P V with the stored entries as the row-major operand (ldmatrix.trans).
-// Three block barriers per tile.  Maxima are kept twice (the tile's old and new one) so that step 3 still finds the
+// Three block barriers per tile (four where two warps share a unit).  Maxima are kept twice (the tile's old and new one) so that step 3 still finds the
 // old one; sums are kept by the rows' own threads.  At the end the sink's term joins the denominator.
 //
-// Launches: sequences that bring one token run with MT = 1 and KT = 64 (16 rows of 16 heads stream a sequence's
-// entries once), their keys split over `num_splits` blocks whose partial results (normalised, with the logarithm
-// of their denominators) a second kernel merges, sink included.  Sequences that bring more run with MT = 4 and
-// KT = 32: four consecutive queries share every tile of keys.
+// Launches: sequences that bring one token run with MT = 1, rounds of 64 keys (two stages of 32) and five slots
+// (16 rows of 16 heads stream a sequence's entries once; three stages are on their way while two are used), their
+// keys split over `num_splits`
+// blocks whose partial results (normalised, with the logarithm of their denominators) a second kernel merges,
+// sink included.  Sequences that bring more run with MT = 4, KT = 32 and three stages: four consecutive queries
+// share every tile of keys.
 #include "attention_mma.cuh"
+#include "tcgen05.cuh"
 
 namespace li {
 
@@ -38,64 +42,107 @@ struct LatentParams {
   float* partial_out;           // [splits][heads][tokens][C] when num_splits > 1
   float* partial_lse;           // [splits][heads][tokens], in units of log2
   int tokens;
+  int* error_flag;              // set to 31 if a wait for a tile of entries ever gave up (may be null)
 };
 
-constexpr int kLatentWarps = 8;
+// One entry (a contiguous run of bytes, 16-byte aligned at both ends) from global into shared memory by the copy
+// engine; its bytes count towards the mbarrier's transaction.
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+constexpr int kLatentWarps = 16;
+constexpr int kTableCache = 2048;   // block-table entries a block keeps in shared memory (more are read in place)
 constexpr int kPad = 8;         // bfloat16 of padding per shared-memory row: rows 16 bytes apart modulo 128
 
-template <int C, int R, int MT, int KT>
+constexpr int kMaxStages = 6;
+
+// KT: keys of one stage (one ring slot); SUB: stages used per round of the loop (KI = SUB * KT keys); NS: slots.
+template <int C, int R, int MT, int KT, int SUB, int NS>
 struct LatentSmem {
-  static constexpr int D = C + R, LD = D + kPad, PLD = KT + kPad;
-  static constexpr int kRows = MT * 16, kUnits = MT * (KT / 8);
+  static constexpr int KI = SUB * KT;
+  static constexpr int D = C + R, LD = D + kPad, PLD = KI + kPad;
+  static constexpr int kRows = MT * 16, kUnits = MT * (KI / 8);
   static constexpr size_t q_bytes = (size_t)kRows * LD * 2;
   static constexpr size_t k_bytes = (size_t)KT * LD * 2;
   static constexpr size_t p_bytes = (size_t)kRows * PLD * 2;
-  static constexpr size_t f_floats = (size_t)kRows * (KT / 8) * 2 + kRows * 4;
-  static constexpr size_t total = q_bytes + 2 * k_bytes + p_bytes + f_floats * 4;
+  static constexpr int kSplitK = kLatentWarps / kUnits;      // warps that share a unit, each with a part of the k-range
+  static_assert(kSplitK * kUnits == kLatentWarps && NS > SUB && NS <= kMaxStages && KT % 16 == 0, "units must deal out evenly");
+  static constexpr size_t f_floats = (size_t)kRows * (KI / 8) * 2 + kRows * 4;
+  static constexpr size_t s_floats = (size_t)(kSplitK - 1) * kRows * KI;      // the other warps' partial scores
+  static constexpr size_t total = q_bytes + NS * k_bytes + p_bytes + (f_floats + s_floats) * 4;
 };
 
+// Called by warp 0: every lane looks its keys up in the block table once; lane 0 tells the stage's mbarrier how
+// many bytes to expect, then every visible entry is ONE bulk copy (no thread computes an address per 16 bytes).
+// An entry that is not visible (behind the last query, or on a page given back) is written as zeros.
 template <int C, int R, int KT>
-__device__ __forceinline__ void load_key_tile(bf16* ks, const LatentParams& p, const int* table, int key0, int limit) {
-  // A warp takes every eighth key: one look at the block table per key, then the lanes fetch the entry's 16-byte
-  // chunks in turn.  An entry that is not visible (behind the last query, or on a page given back) arrives as zeros.
-  constexpr int D = C + R, LD = D + kPad, kChunks = D / 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int key = warp; key < KT; key += kLatentWarps) {
-    const int kpos = key0 + key;
-    bool valid = kpos < limit;
-    const bf16* src = p.pool;
-    if (valid) {
-      const int page = table[kpos / p.page_size];
-      valid = page >= 0 && page < p.num_pages;
-      if (valid) src = p.pool + ((size_t)page * p.page_size + kpos % p.page_size) * D;
-    }
-    bf16* dst = ks + key * LD;
+__device__ __forceinline__ void load_key_tile(bf16* ks, unsigned bar, const LatentParams& p, const int* table,
+                                              const int* cached, int cached_first, int cached_count, int key0,
+                                              int limit) {
+  constexpr int D = C + R, LD = D + kPad;
+  constexpr unsigned kRowBytes = D * 2;
+  const int lane = threadIdx.x & 31;
+  const bf16* src[KT / 32];
+  int count = 0;
 #pragma unroll
-    for (int chunk = lane; chunk < kChunks; chunk += 32) cp_async16(dst + chunk * 8, src + (valid ? chunk * 8 : 0), valid);
+  for (int j = 0; j < KT / 32; ++j) {
+    const int kpos = key0 + lane + 32 * j;
+    src[j] = nullptr;
+    if (kpos < limit) {
+      // The block's part of the block table lies in shared memory (its first `cached_count` entries from
+      // `cached_first` on); a look-up there does not hold the copies up for a trip to memory.
+      const int block = kpos / p.page_size, at = block - cached_first;
+      const int page = at < cached_count ? cached[at] : table[block];
+      if (page >= 0 && page < p.num_pages) src[j] = p.pool + ((size_t)page * p.page_size + kpos % p.page_size) * D;
+    }
+    count += src[j] != nullptr;
+  }
+  count = __reduce_add_sync(0xffffffffu, count);
+  if (lane == 0) mbar_expect_tx(bar, (unsigned)count * kRowBytes);
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < KT / 32; ++j) {
+    bf16* dst = ks + (lane + 32 * j) * LD;
+    if (src[j]) {
+      bulk_load(smem_addr(dst), src[j], kRowBytes, bar);
+    } else {
+      for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+      fence_async_shared();       // a later bulk copy into this row comes behind these stores
+    }
   }
 }
 
-template <int C, int R, int MT, int KT>
+template <int C, int R, int MT, int KT, int SUB, int NS>
 __global__ void __launch_bounds__(kLatentWarps * 32, 1)
 latent_attention_mma_kernel(const LatentParams p) {
-  using S = LatentSmem<C, R, MT, KT>;
-  constexpr int D = S::D, LD = S::LD, PLD = S::PLD, kRows = S::kRows, kNTiles = KT / 8;
-  constexpr int kOwn = C / kLatentWarps;         // numbers of the accumulator a warp owns
+  using S = LatentSmem<C, R, MT, KT, SUB, NS>;
+  constexpr int KI = S::KI;
+  constexpr int D = S::D, LD = S::LD, PLD = S::PLD, kRows = S::kRows, kNTiles = KI / 8;
+  constexpr int kOwnWarps = C / 8 < kLatentWarps ? C / 8 : kLatentWarps;   // warps that own a share of the accumulators
+  constexpr int kOwn = C / kOwnWarps;            // numbers of the accumulator such a warp owns
   constexpr int kOwnTiles = kOwn / 8;
+  constexpr int kSplitK = S::kSplitK;
+  constexpr int kChunks32 = D / 32;              // the k-range in runs of 32 numbers, dealt to the warps of a unit
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);
   bf16* ks0 = reinterpret_cast<bf16*>(smem_raw + S::q_bytes);
-  bf16* ps = reinterpret_cast<bf16*>(smem_raw + S::q_bytes + 2 * S::k_bytes);
-  float* unit_max = reinterpret_cast<float*>(smem_raw + S::q_bytes + 2 * S::k_bytes + S::p_bytes);   // [kNTiles][kRows]
+  bf16* ps = reinterpret_cast<bf16*>(smem_raw + S::q_bytes + NS * S::k_bytes);
+  float* unit_max = reinterpret_cast<float*>(smem_raw + S::q_bytes + NS * S::k_bytes + S::p_bytes);   // [kNTiles][kRows]
   float* unit_sum = unit_max + kNTiles * kRows;                                                       // [kNTiles][kRows]
   float* row_max = unit_sum + kNTiles * kRows;                                                        // [2][kRows]
   float* row_sum = row_max + 2 * kRows;                                                               // [kRows]
   float* row_inv = row_sum + kRows;                                                                   // [kRows]
+  float* half_scores = row_inv + kRows;                                                               // [kSplitK - 1][kRows][KI]
 
+  __shared__ __align__(8) unsigned long long stage_bars[kMaxStages];
+  __shared__ int table_cache[kTableCache];
   grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int split = p.num_splits > 1 ? blockIdx.x % p.num_splits : 0;
-  const int tile_index = p.num_splits > 1 ? blockIdx.x / p.num_splits : blockIdx.x;
+  // Blocks with the most keys first (a prompt's last queries): the short ones fill the end of the launch.
+  const int tile_index = p.num_splits > 1 ? blockIdx.x / p.num_splits : gridDim.x - 1 - blockIdx.x;
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
   if (seq < 0) return;
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
@@ -106,13 +153,31 @@ latent_attention_mma_kernel(const LatentParams p) {
   const int* table = p.block_table + (size_t)seq * p.table_stride;
   const int first_pos = ctx - q_len + query0;                        // position of the block's first query
   const int last_pos = min(first_pos + MT - 1, ctx - 1);             // of its last one: the keys end there
-  const int all_tiles = last_pos / KT + 1;
+  const int all_tiles = last_pos / KI + 1;                           // rounds of KI keys
   const int per_split = (all_tiles + p.num_splits - 1) / p.num_splits;
   const int tile_begin = split * per_split, tile_end = min(all_tiles, tile_begin + per_split);
 
+  const unsigned bars = smem_addr(stage_bars);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) mbar_init(bars + 8 * i, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // The part of the block table that this block walks (an input of the step, not of a kernel ahead).
+  const int cached_first = tile_begin * KI / p.page_size;
+  const int cached_count = tile_begin < tile_end ? min(kTableCache, (min(tile_end * KI, last_pos + 1) - 1) / p.page_size + 1 - cached_first) : 0;
+  for (int i = threadIdx.x; i < cached_count; i += kLatentWarps * 32) table_cache[i] = table[cached_first + i];
+  __syncthreads();
   grid_dependency_wait();      // the entries of this step's tokens and the queries come from kernels ahead
-  if (tile_begin < tile_end) load_key_tile<C, R, KT>(ks0, p, table, tile_begin * KT, last_pos + 1);
-  cp_async_commit();
+  // Stage r of this block (r = 0, 1, ...) holds keys [(tile_begin * SUB + r) * KT, + KT), lies in slot r % NS and
+  // turns that slot's barrier for the (r / NS)-th time.  A stage behind the last key is still "loaded": its rows are
+  // written as zeros and its barrier turns, so the loop needs no special case for it.
+  const int stages_total = (tile_end - tile_begin) * SUB;
+  if (warp == 0) {             // every slot filled before the first round
+    for (int r = 0; r < NS && r < stages_total; ++r)
+      load_key_tile<C, R, KT>(ks0 + (size_t)r * KT * LD, bars + 8 * r, p, table, table_cache, cached_first, cached_count,
+                              (tile_begin * SUB + r) * KT, last_pos + 1);
+  }
 
   // The query rows: row 16 * i + j is head head0 + j of query query0 + i; [absorbed query | rotated part].
   for (int i = threadIdx.x; i < kRows * (C / 8); i += kLatentWarps * 32) {
@@ -161,39 +226,49 @@ latent_attention_mma_kernel(const LatentParams p) {
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int it = tile - tile_begin;
-    bf16* ks = ks0 + (size_t)(it & 1) * KT * LD;
-    bf16* ks_next = ks0 + (size_t)((it + 1) & 1) * KT * LD;
-    if (tile + 1 < tile_end) load_key_tile<C, R, KT>(ks_next, p, table, (tile + 1) * KT, last_pos + 1);
-    cp_async_commit();
-    cp_async_wait<1>();           // this tile's entries have landed (the next one's may be on their way)
-    __syncthreads();
+    if (warp == 0 && it > 0) {          // the slots that the round before this one used are free: fill them again
+#pragma unroll
+      for (int j = 0; j < SUB; ++j) {
+        const int r = (it - 1) * SUB + j + NS;
+        if (r < stages_total)
+          load_key_tile<C, R, KT>(ks0 + (size_t)(r % NS) * KT * LD, bars + 8 * (r % NS), p, table, table_cache, cached_first,
+                                  cached_count, (tile_begin * SUB + r) * KT, last_pos + 1);
+      }
+    }
+    // This tile's entries have landed when its stage's barrier has turned (the next one's may be on their way).  A
+    // wait that runs out raises the error flag; the block then stops, all of its threads together.
+    bool landed = true;
+#pragma unroll
+    for (int j = 0; j < SUB; ++j) {
+      const int r = it * SUB + j;
+      landed = mbar_wait(bars + 8 * (r % NS), (unsigned)(r / NS) & 1, p.error_flag, 31) && landed;
+    }
+    if (__syncthreads_or(!landed)) break;
     const float* old_max = row_max + (it & 1) * kRows;
     float* new_max = row_max + ((it + 1) & 1) * kRows;
-    const int key0 = tile * KT;
+    const int key0 = tile * KI;
 
-    // 1. scores of this warp's units, kept in registers: unit u = (row tile u / kNTiles, keys 8 * (u % kNTiles)...).
-    constexpr int kUnitsPerWarp = (S::kUnits + kLatentWarps - 1) / kLatentWarps;
-    float sc[kUnitsPerWarp][4];
-#pragma unroll
-    for (int uu = 0; uu < kUnitsPerWarp; ++uu) {
-      const int u = warp + uu * kLatentWarps;
-      sc[uu][0] = sc[uu][1] = sc[uu][2] = sc[uu][3] = 0.f;
-      if (u >= S::kUnits) continue;
-      const int mt = u / kNTiles, nt = u % kNTiles;
+    // 1. scores: unit u = (row tile u / kNTiles, keys 8 * (u % kNTiles)...) belongs to warp u, or to warps u,
+    //    u + units, ..., which then take a part of the k-range each and add their parts through shared memory.
+    const int u = warp % S::kUnits, khalf = warp / S::kUnits;
+    const int mt = u / kNTiles, nt = u % kNTiles;
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    {
       const bf16* qa = qs + (mt * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
-      const bf16* kb = ks + (nt * 8 + (lane & 7)) * LD + (lane >> 3) * 8;
+      const bf16* kb = ks0 + (size_t)((it * SUB + nt * 8 / KT) % NS) * KT * LD + (nt * 8 % KT + (lane & 7)) * LD + (lane >> 3) * 8;
+      const int k_begin = (khalf * kChunks32 / kSplitK) * 32, k_end = ((khalf + 1) * kChunks32 / kSplitK) * 32;
       // Four partial sums, each over every fourth k-step: the products of one sum wait for each other, not for
       // the other three's.
       float part[3][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll 3
-      for (int k0 = 0; k0 < D; k0 += 64) {
+      for (int k0 = k_begin; k0 < k_end; k0 += 64) {
         unsigned a[4], a2[4], b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3, kb + k0);          // keys nt*8.., numbers k0..k0+31: two k-steps
         ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
         ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
-        mma_bf16(sc[uu], a, b0, b1);
+        mma_bf16(sc, a, b0, b1);
         mma_bf16(part[0], a2, b2, b3);
-        if (k0 + 32 < D) {
+        if (k0 + 32 < k_end) {
           ldmatrix_x4(b0, b1, b2, b3, kb + k0 + 32);
           ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0 + 32);
           ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 48);
@@ -202,16 +277,34 @@ latent_attention_mma_kernel(const LatentParams p) {
         }
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) sc[uu][e] += part[0][e] + part[1][e] + part[2][e];
+      for (int e = 0; e < 4; ++e) sc[e] += part[0][e] + part[1][e] + part[2][e];
+    }
+    if (kSplitK > 1) {
+      float* lo = half_scores + (mt * 16 + g) * KI + nt * 8 + 2 * t4;
+      if (khalf > 0) {
+        *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI) = make_float2(sc[0], sc[1]);
+        *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI + 8 * KI) = make_float2(sc[2], sc[3]);
+      }
+      __syncthreads();
+      if (khalf == 0) {
+#pragma unroll
+        for (int part = 0; part < kSplitK - 1; ++part) {
+          const float2 x = *reinterpret_cast<const float2*>(lo + part * kRows * KI);
+          const float2 y = *reinterpret_cast<const float2*>(lo + part * kRows * KI + 8 * KI);
+          sc[0] += x.x; sc[1] += x.y; sc[2] += y.x; sc[3] += y.y;
+        }
+      }
+    }
+    if (khalf == 0) {
       // Scale, mask (key j is visible to the query at position pos iff j <= pos), and the unit's row maxima.
       const int pos = first_pos + mt;
       const int kcol = key0 + nt * 8 + 2 * t4;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = kcol + (e & 1);
-        sc[uu][e] = key <= pos ? sc[uu][e] * p.scale_log2 : -INFINITY;
+        sc[e] = key <= pos ? sc[e] * p.scale_log2 : -INFINITY;
       }
-      float m_lo = fmaxf(sc[uu][0], sc[uu][1]), m_hi = fmaxf(sc[uu][2], sc[uu][3]);
+      float m_lo = fmaxf(sc[0], sc[1]), m_hi = fmaxf(sc[2], sc[3]);
       m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
       m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
       m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
@@ -230,11 +323,7 @@ latent_attention_mma_kernel(const LatentParams p) {
       for (int n = 0; n < kNTiles; ++n) m = fmaxf(m, unit_max[n * kRows + threadIdx.x]);
       new_max[threadIdx.x] = m;
     }
-#pragma unroll
-    for (int uu = 0; uu < kUnitsPerWarp; ++uu) {
-      const int u = warp + uu * kLatentWarps;
-      if (u >= S::kUnits) continue;
-      const int mt = u / kNTiles, nt = u % kNTiles;
+    if (khalf == 0) {
       const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
       float m_lo = old_max[r_lo], m_hi = old_max[r_hi];
 #pragma unroll
@@ -242,10 +331,10 @@ latent_attention_mma_kernel(const LatentParams p) {
         m_lo = fmaxf(m_lo, unit_max[n * kRows + r_lo]);
         m_hi = fmaxf(m_hi, unit_max[n * kRows + r_hi]);
       }
-      const float p0 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[uu][0] - m_lo);
-      const float p1 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[uu][1] - m_lo);
-      const float p2 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[uu][2] - m_hi);
-      const float p3 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[uu][3] - m_hi);
+      const float p0 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[0] - m_lo);
+      const float p1 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[1] - m_lo);
+      const float p2 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[2] - m_hi);
+      const float p3 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[3] - m_hi);
       *reinterpret_cast<__nv_bfloat162*>(ps + r_lo * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p0, p1);
       *reinterpret_cast<__nv_bfloat162*>(ps + r_hi * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p2, p3);
       float s_lo = p0 + p1, s_hi = p2 + p3;
@@ -271,6 +360,7 @@ latent_attention_mma_kernel(const LatentParams p) {
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
+      if (warp >= kOwnWarps) break;
       const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
       const float n_lo = new_max[r_lo], n_hi = new_max[r_hi];
       const float a_lo = n_lo == -INFINITY ? 1.f : fast_exp2(old_max[r_lo] - n_lo);
@@ -284,10 +374,11 @@ latent_attention_mma_kernel(const LatentParams p) {
       }
       const bf16* pa = ps + (mt * 16 + (lane & 15)) * PLD + (lane >> 4) * 8;
 #pragma unroll
-      for (int k0 = 0; k0 < KT; k0 += 16) {
+      for (int k0 = 0; k0 < KI; k0 += 16) {
         unsigned a[4];
         ldmatrix_x4(a[0], a[1], a[2], a[3], pa + k0);
-        const bf16* vb = ks + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + warp * kOwn + (lane >> 4) * 8;
+        const bf16* vb = ks0 + (size_t)((it * SUB + k0 / KT) % NS) * KT * LD +
+                         (k0 % KT + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + warp * kOwn + (lane >> 4) * 8;
 #pragma unroll
         for (int n = 0; n < kOwnTiles; n += 2) {
           unsigned b0, b1, b2, b3;
@@ -299,10 +390,8 @@ latent_attention_mma_kernel(const LatentParams p) {
     }
     __syncthreads();      // the probabilities and this stage of entries may be overwritten
   }
-  cp_async_wait<0>();
-
   // The end: denominators (with the sink's term where this block sees all keys), then the rows leave.
-  const int final_buf = ((tile_end > tile_begin ? tile_end - tile_begin : 0) & 1) * kRows;
+  const int final_buf = ((tile_end > tile_begin ? tile_end - tile_begin : 0) & 1) * kRows;   // where the last tile left the maxima
   if (threadIdx.x < kRows) {
     const int head = head0 + threadIdx.x % 16;
     float m = row_max[final_buf + threadIdx.x], l = row_sum[threadIdx.x];
@@ -327,7 +416,7 @@ latent_attention_mma_kernel(const LatentParams p) {
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     const int query = query0 + mt;
-    if (query >= q_len) continue;
+    if (query >= q_len || warp >= kOwnWarps) continue;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int head = head0 + g + hh * 8;
@@ -350,52 +439,69 @@ latent_attention_mma_kernel(const LatentParams p) {
 }
 
 // The splits of a (token, head) row merged: out = sum_s w_s O_s / (sum_s w_s + the sink's term), w_s = 2^(lse_s - max).
+// The weights are worked out once per block; a thread then adds up its numbers with all loads on their way at once.
+constexpr int kMaxSplits = 32;
 __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
                                     const int* __restrict__ seq_index, const int* __restrict__ query_start_loc,
                                     bf16* __restrict__ out, long out_head_stride,
                                     int out_token_stride, const float* __restrict__ sink, int heads, int tokens,
                                     int C, int num_splits) {
+  __shared__ float weight[kMaxSplits];
   grid_dependency_wait();
   grid_launch_dependents();
   const int seq = seq_index ? seq_index[blockIdx.x] : blockIdx.x;
   const int head = blockIdx.y;
   if (seq < 0) return;                            // a place of padding
   const int token = query_start_loc[seq];         // the sequence's one token
-  float m = sink ? sink[head] * kLog2e : -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, partial_lse[((size_t)s * heads + head) * tokens + token]);
-  float denom = sink ? exp2f(sink[head] * kLog2e - m) : 0.f;
-  for (int s = 0; s < num_splits; ++s) denom += exp2f(partial_lse[((size_t)s * heads + head) * tokens + token] - m);
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int d = threadIdx.x; d < C; d += blockDim.x) {
-    float v = 0.f;
+  if (threadIdx.x < 32) {
+    const float sk = sink ? sink[head] * kLog2e : -INFINITY;
+    const float lse = (int)threadIdx.x < num_splits
+                          ? partial_lse[((size_t)threadIdx.x * heads + head) * tokens + token] : -INFINITY;
+    float m = fmaxf(lse, sk);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float w = m == -INFINITY ? 0.f : exp2f(lse - m);
+    float denom = w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (sink && m != -INFINITY) denom += exp2f(sk - m);
+    weight[threadIdx.x] = denom > 0.f ? w / denom : 0.f;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x * 4; d < C; d += blockDim.x * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
     for (int s = 0; s < num_splits; ++s) {
-      const size_t row = ((size_t)s * heads + head) * tokens + token;
-      const float w = exp2f(partial_lse[row] - m);
-      if (w > 0.f) v = fmaf(w, partial_out[row * C + d], v);
+      const float w = weight[s];
+      const float4 x = *reinterpret_cast<const float4*>(partial_out + (((size_t)s * heads + head) * tokens + token) * C + d);
+      v.x = fmaf(w, x.x, v.x); v.y = fmaf(w, x.y, v.y); v.z = fmaf(w, x.z, v.z); v.w = fmaf(w, x.w, v.w);
     }
-    out[(size_t)head * out_head_stride + (size_t)token * out_token_stride + d] = __float2bfloat16_rn(v * inv);
+    bf16* o = out + (size_t)head * out_head_stride + (size_t)token * out_token_stride + d;
+    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(v.z, v.w);
   }
 }
 
-template <int C, int R, int MT, int KT>
+template <int C, int R, int MT, int KT, int SUB, int NS>
 int launch_latent(const LatentParams& p, int num_seqs, int row_tiles, cudaStream_t stream) {
-  using S = LatentSmem<C, R, MT, KT>;
+  using S = LatentSmem<C, R, MT, KT, SUB, NS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT>,
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT, SUB, NS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::total);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(row_tiles * (p.num_splits > 1 ? p.num_splits : 1), (p.heads + 15) / 16, num_seqs);
-  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT>, grid, dim3(kLatentWarps * 32),
+  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT, SUB, NS>, grid, dim3(kLatentWarps * 32),
                          S::total, stream, p);
 }
 
 template <int C, int R>
 int launch_latent_sizes(const LatentParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
-  if (max_q_len == 1) return launch_latent<C, R, 1, 64>(p, num_seqs, 1, stream);
-  return launch_latent<C, R, 4, 32>(p, num_seqs, (max_q_len + 3) / 4, stream);
+  // Stages of entries on their way: as many as shared memory holds beside the query rows.
+  if (max_q_len == 1) return launch_latent<C, R, 1, 32, 2, 5>(p, num_seqs, 1, stream);
+  return launch_latent<C, R, 4, 32, 1, 3>(p, num_seqs, (max_q_len + 3) / 4, stream);
 }
 
 }  // namespace li
@@ -411,7 +517,8 @@ LI_EXPORT int li_latent_attention_mma_supports(int kv_rank, int rot_dim, int rot
 // As li_latent_attention (attention_latent.cu), bfloat16 only, for the sizes `..._supports` names.  seq_index
 // [num_seqs] or null: the batch rows to run (-1: none); max_q_len 1 runs the single-token form, whose keys
 // `num_splits` blocks share (partial_out [splits, heads, tokens, kv_rank] and partial_lse [splits, heads, tokens]
-// float; `tokens`: the step's token rows).
+// float; `tokens`: the step's token rows).  error_flag (device int, zero; may be null): set to 31 if a wait for a
+// tile of entries ever gave up.
 LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
                                       const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
                                       void* out, long out_head_stride, int out_token_stride, const void* pool,
@@ -420,13 +527,14 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
                                       const float* sink, int num_seqs, int max_q_len, int heads, int kv_rank,
                                       int rot_dim, int rot_dims, int page_size, int num_pages, float scale,
                                       int num_splits, float* partial_out, float* partial_lse, int tokens,
-                                      cudaStream_t stream) {
+                                      int* error_flag, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (!li_latent_attention_mma_supports(kv_rank, rot_dim, rot_dims) || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
   if (!aligned16(q_lat) || !aligned16(pool) || (q_lat_token_stride % 8) || (q_lat_head_stride % 8) || (out_token_stride % 2) ||
       (out_head_stride % 2))
     return LI_ERR_ALIGNMENT;
   if (max_q_len != 1) num_splits = 1;
+  if (num_splits > kMaxSplits) num_splits = kMaxSplits;
   if (num_splits > 1 && (!partial_out || !partial_lse)) return LI_ERR_UNSUPPORTED;
   LatentParams p;
   p.q_lat = (const bf16*)q_lat; p.q_lat_head_stride = q_lat_head_stride; p.q_lat_token_stride = q_lat_token_stride;
@@ -437,7 +545,7 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
   p.query_start_loc = query_start_loc; p.context_lens = context_lens; p.seq_index = seq_index;
   p.inv_freq = inv_freq; p.sink = sink; p.heads = heads; p.rot_dims = rot_dims; p.page_size = page_size;
   p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.num_splits = num_splits < 1 ? 1 : num_splits;
-  p.partial_out = partial_out; p.partial_lse = partial_lse; p.tokens = tokens;
+  p.partial_out = partial_out; p.partial_lse = partial_lse; p.tokens = tokens; p.error_flag = error_flag;
   int code;
   if (kv_rank == 64) code = launch_latent_sizes<64, 32>(p, num_seqs, max_q_len, stream);
   else if (kv_rank == 128 && rot_dim == 32) code = launch_latent_sizes<128, 32>(p, num_seqs, max_q_len, stream);

@@ -108,7 +108,7 @@ _SIGNATURES = {
     "li_latent_attention_mma": ("attention_latent_mma", [
         c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-        c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+        c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "li_latent_attention_mma_supports": ("attention_latent_mma", [c_int, c_int, c_int]),
     "li_gate_heads": ("attention_latent", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1226,7 +1226,8 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
                 q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
                 block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), _ptr(seq_index),
                 inv_freq.data_ptr(), _ptr(sink), count, q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages,
-                float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens, _stream()),
+                float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens,
+                scratch_for(out.device).gemm_error.data_ptr(), _stream()),
                 "latent_attention_mma")
 
         if plan is None:
@@ -1236,7 +1237,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
             run(plan.prefill_seqs, plan.num_prefill, max(plan.max_prefill_query_len, 2))
         if plan.num_decode:
             chunks = -(-heads // 16)
-            tiles = max(1, -(-plan.max_decode_context_len // 64))
+            tiles = max(1, -(-plan.max_decode_context_len // 64))            # two tiles of 32 keys a split at least
             # One block per SM (a block's two stages of entries fill most of its shared memory): as many splits
             # as still make one wave.
             splits = max(1, min(tiles, NUM_SMS // max(1, plan.num_decode * chunks), 32))
