@@ -1252,11 +1252,16 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
     return out
 
 
+# (latent, rotated part) that attention_latent_mma.cu is instantiated for (its own `..._supports` says the same; the
+# table stands here too so that a model of other sizes never builds that library).
+_LATENT_MMA_SIZES = {(64, 32), (128, 32), (128, 64), (256, 64), (512, 64)}
+
+
 def latent_mma_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int, rot_dims: int) -> bool:
     """Whether the tensor-core latent attention takes these sizes (bfloat16; LITEINFER_LATENT_MMA=0 keeps every
     size on the SIMT kernel)."""
     return (dtype == torch.bfloat16 and os.environ.get("LITEINFER_LATENT_MMA", "1") != "0"
-            and bool(_fn("li_latent_attention_mma_supports")(kv_rank, rot_dim, rot_dims)))
+            and (kv_rank, rot_dim) in _LATENT_MMA_SIZES and 0 <= rot_dims <= rot_dim and rot_dims % 2 == 0)
 
 
 def gate_heads(v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
