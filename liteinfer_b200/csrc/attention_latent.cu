@@ -80,11 +80,11 @@ latent_prep_kernel(const T* __restrict__ proj, int proj_stride, int q_off, int q
 }
 
 // ------------------------------------------------------------------------------------- attention
-constexpr int kMaxLatent = 512;             // most values per entry the SIMT kernel accumulates (16 per lane)
+constexpr int kMaxLatent = 1024;            // most values per entry the SIMT kernel accumulates (16 or 32 per lane)
 constexpr int kLatentQueriesPerBlock = 4;
 constexpr int kLatentHeadsPerBlock = 8;
 
-template <typename T>
+template <typename T, int kPerLane>
 __global__ void __launch_bounds__(256)
 latent_attention_kernel(const T* __restrict__ q_lat, long q_lat_head_stride, int q_lat_token_stride,
                         const T* __restrict__ q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
@@ -108,7 +108,6 @@ latent_attention_kernel(const T* __restrict__ q_lat, long q_lat_head_stride, int
   const int entry_dim = kv_rank + rot_dim;
   float* qs = q_smem + warp * entry_dim;
   const int* table = block_table + (size_t)seq * table_stride;
-  constexpr int kPerLane = kMaxLatent / 32;
   const int half = rot_dims / 2;
   grid_dependency_wait();
 
@@ -257,18 +256,18 @@ LI_EXPORT int li_latent_attention(int dtype, const void* q_lat, long q_lat_head_
                   (heads + kLatentHeadsPerBlock - 1) / kLatentHeadsPerBlock, num_seqs);
   const size_t smem = (size_t)(threads / 32) * (kv_rank + rot_dim) * sizeof(float);
   cudaError_t e;
-  if (dtype == kFloat32)
-    e = launch_pdl(max_q_len, latent_attention_kernel<float>, grid, dim3(threads), smem, stream, (const float*)q_lat,
-                   q_lat_head_stride, q_lat_token_stride, (const float*)q_raw, q_raw_token_stride, q_raw_head_stride,
-                   q_rot_off, (float*)out, out_head_stride, out_token_stride, (const float*)pool, block_table,
-                   table_stride, query_start_loc, context_lens, inv_freq, sink, heads, kv_rank, rot_dim, rot_dims,
-                   page_size, num_pages, scale);
-  else
-    e = launch_pdl(max_q_len, latent_attention_kernel<bf16>, grid, dim3(threads), smem, stream, (const bf16*)q_lat,
-                   q_lat_head_stride, q_lat_token_stride, (const bf16*)q_raw, q_raw_token_stride, q_raw_head_stride,
-                   q_rot_off, (bf16*)out, out_head_stride, out_token_stride, (const bf16*)pool, block_table,
-                   table_stride, query_start_loc, context_lens, inv_freq, sink, heads, kv_rank, rot_dim, rot_dims,
-                   page_size, num_pages, scale);
+#define LI_LATENT_LAUNCH(T, N)                                                                                        \
+  e = launch_pdl(max_q_len, latent_attention_kernel<T, N>, grid, dim3(threads), smem, stream, (const T*)q_lat,        \
+                 q_lat_head_stride, q_lat_token_stride, (const T*)q_raw, q_raw_token_stride, q_raw_head_stride,       \
+                 q_rot_off, (T*)out, out_head_stride, out_token_stride, (const T*)pool, block_table, table_stride,    \
+                 query_start_loc, context_lens, inv_freq, sink, heads, kv_rank, rot_dim, rot_dims, page_size,         \
+                 num_pages, scale)
+  if (dtype == kFloat32) {
+    if (kv_rank <= 512) LI_LATENT_LAUNCH(float, 16); else LI_LATENT_LAUNCH(float, 32);
+  } else {
+    if (kv_rank <= 512) LI_LATENT_LAUNCH(bf16, 16); else LI_LATENT_LAUNCH(bf16, 32);
+  }
+#undef LI_LATENT_LAUNCH
   return (int)e;
 }
 

@@ -2,7 +2,7 @@
 // shared cache entries [latent (C) | rotated key part (R)], whose first C numbers are also the values
 // (attention_latent.cu has the formulas and the SIMT kernel for every other size and for float32).
 //
-// A block of sixteen warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
+// A block of sixteen (or eight) warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
 // the keys KT at a time (one bulk copy per entry into padded shared memory, a ring of stages behind mbarriers, the next
 // tiles on their way while this one is used).  Per tile of keys:
 //   1. scores: the MT x (KT / 8) units of 16 rows x 8 keys are dealt to the warps, one unit a warp, or two warps a
@@ -16,9 +16,9 @@
 // Three block barriers per tile (four where two warps share a unit).  Maxima are kept twice (the tile's old and new one) so that step 3 still finds the
 // old one; sums are kept by the rows' own threads.  At the end the sink's term joins the denominator.
 //
-// Launches: sequences that bring one token run with MT = 1, rounds of 64 keys (two stages of 32) and five slots
-// (16 rows of 16 heads stream a sequence's entries once; three stages are on their way while two are used), their
-// keys split over `num_splits`
+// Launches: sequences that bring one token run with MT = 1 (16 rows of 16 heads stream a sequence's entries
+// once), either as two blocks of eight warps per SM (rounds of 32 keys, two stages) or as one block of sixteen
+// warps (rounds of 64 keys from five stages of 32), their keys split over `num_splits`
 // blocks whose partial results (normalised, with the logarithm of their denominators) a second kernel merges,
 // sink included.  Sequences that bring more run with MT = 4, KT = 32 and three stages: four consecutive queries
 // share every tile of keys.
@@ -52,14 +52,14 @@ __device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigne
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-constexpr int kLatentWarps = 16;
+constexpr int kMaxLatentWarps = 16;
 constexpr int kTableCache = 2048;   // block-table entries a block keeps in shared memory (more are read in place)
 constexpr int kPad = 8;         // bfloat16 of padding per shared-memory row: rows 16 bytes apart modulo 128
 
 constexpr int kMaxStages = 6;
 
 // KT: keys of one stage (one ring slot); SUB: stages used per round of the loop (KI = SUB * KT keys); NS: slots.
-template <int C, int R, int MT, int KT, int SUB, int NS>
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
 struct LatentSmem {
   static constexpr int KI = SUB * KT;
   static constexpr int D = C + R, LD = D + kPad, PLD = KI + kPad;
@@ -67,8 +67,8 @@ struct LatentSmem {
   static constexpr size_t q_bytes = (size_t)kRows * LD * 2;
   static constexpr size_t k_bytes = (size_t)KT * LD * 2;
   static constexpr size_t p_bytes = (size_t)kRows * PLD * 2;
-  static constexpr int kSplitK = kLatentWarps / kUnits;      // warps that share a unit, each with a part of the k-range
-  static_assert(kSplitK * kUnits == kLatentWarps && NS > SUB && NS <= kMaxStages && KT % 16 == 0, "units must deal out evenly");
+  static constexpr int kSplitK = NW / kUnits;      // warps that share a unit, each with a part of the k-range
+  static_assert(kSplitK * kUnits == NW && NW <= kMaxLatentWarps && NS > SUB && NS <= kMaxStages && KT % 16 == 0, "units must deal out evenly");
   static constexpr size_t f_floats = (size_t)kRows * (KI / 8) * 2 + kRows * 4;
   static constexpr size_t s_floats = (size_t)(kSplitK - 1) * kRows * KI;      // the other warps' partial scores
   static constexpr size_t total = q_bytes + NS * k_bytes + p_bytes + (f_floats + s_floats) * 4;
@@ -114,10 +114,11 @@ __device__ __forceinline__ void load_key_tile(bf16* ks, unsigned bar, const Late
   }
 }
 
-template <int C, int R, int MT, int KT, int SUB, int NS>
-__global__ void __launch_bounds__(kLatentWarps * 32, 1)
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
+__global__ void __launch_bounds__(NW * 32, NW <= 8 ? 2 : 1)
 latent_attention_mma_kernel(const LatentParams p) {
-  using S = LatentSmem<C, R, MT, KT, SUB, NS>;
+  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW>;
+  constexpr int kLatentWarps = NW;
   constexpr int KI = S::KI;
   constexpr int D = S::D, LD = S::LD, PLD = S::PLD, kRows = S::kRows, kNTiles = KI / 8;
   constexpr int kOwnWarps = C / 8 < kLatentWarps ? C / 8 : kLatentWarps;   // warps that own a share of the accumulators
@@ -482,26 +483,32 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const
   }
 }
 
-template <int C, int R, int MT, int KT, int SUB, int NS>
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
 int launch_latent(const LatentParams& p, int num_seqs, int row_tiles, cudaStream_t stream) {
-  using S = LatentSmem<C, R, MT, KT, SUB, NS>;
+  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT, SUB, NS>,
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::total);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(row_tiles * (p.num_splits > 1 ? p.num_splits : 1), (p.heads + 15) / 16, num_seqs);
-  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT, SUB, NS>, grid, dim3(kLatentWarps * 32),
+  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW>, grid, dim3(NW * 32),
                          S::total, stream, p);
 }
 
 template <int C, int R>
-int launch_latent_sizes(const LatentParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
+int launch_latent_sizes(const LatentParams& p, int num_seqs, int max_q_len, int two_blocks, cudaStream_t stream) {
   // Stages of entries on their way: as many as shared memory holds beside the query rows.
-  if (max_q_len == 1) return launch_latent<C, R, 1, 32, 2, 5>(p, num_seqs, 1, stream);
-  return launch_latent<C, R, 4, 32, 1, 3>(p, num_seqs, (max_q_len + 3) / 4, stream);
+  if (max_q_len == 1) {
+    // Two blocks of eight warps per SM (rounds of 32 keys, two stages each): while one block stands at a barrier
+    // the other works.  Or one block of sixteen warps (rounds of 64 keys from five stages of 32): fewer, longer
+    // blocks, which a narrow batch with many splits does a little better with.
+    if (two_blocks) return launch_latent<C, R, 1, 32, 1, 2, 8>(p, num_seqs, 1, stream);
+    return launch_latent<C, R, 1, 32, 2, 5, 16>(p, num_seqs, 1, stream);
+  }
+  return launch_latent<C, R, 4, 32, 1, 3, 16>(p, num_seqs, (max_q_len + 3) / 4, stream);
 }
 
 }  // namespace li
@@ -517,7 +524,7 @@ LI_EXPORT int li_latent_attention_mma_supports(int kv_rank, int rot_dim, int rot
 // As li_latent_attention (attention_latent.cu), bfloat16 only, for the sizes `..._supports` names.  seq_index
 // [num_seqs] or null: the batch rows to run (-1: none); max_q_len 1 runs the single-token form, whose keys
 // `num_splits` blocks share (partial_out [splits, heads, tokens, kv_rank] and partial_lse [splits, heads, tokens]
-// float; `tokens`: the step's token rows).  error_flag (device int, zero; may be null): set to 31 if a wait for a
+// float; `tokens`: the step's token rows; `two_blocks`: the single-token form as two blocks of eight warps per SM).  error_flag (device int, zero; may be null): set to 31 if a wait for a
 // tile of entries ever gave up.
 LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
                                       const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
@@ -527,7 +534,7 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
                                       const float* sink, int num_seqs, int max_q_len, int heads, int kv_rank,
                                       int rot_dim, int rot_dims, int page_size, int num_pages, float scale,
                                       int num_splits, float* partial_out, float* partial_lse, int tokens,
-                                      int* error_flag, cudaStream_t stream) {
+                                      int two_blocks, int* error_flag, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (!li_latent_attention_mma_supports(kv_rank, rot_dim, rot_dims) || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
   if (!aligned16(q_lat) || !aligned16(pool) || (q_lat_token_stride % 8) || (q_lat_head_stride % 8) || (out_token_stride % 2) ||
@@ -547,11 +554,11 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
   p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.num_splits = num_splits < 1 ? 1 : num_splits;
   p.partial_out = partial_out; p.partial_lse = partial_lse; p.tokens = tokens; p.error_flag = error_flag;
   int code;
-  if (kv_rank == 64) code = launch_latent_sizes<64, 32>(p, num_seqs, max_q_len, stream);
-  else if (kv_rank == 128 && rot_dim == 32) code = launch_latent_sizes<128, 32>(p, num_seqs, max_q_len, stream);
-  else if (kv_rank == 128) code = launch_latent_sizes<128, 64>(p, num_seqs, max_q_len, stream);
-  else if (kv_rank == 256) code = launch_latent_sizes<256, 64>(p, num_seqs, max_q_len, stream);
-  else code = launch_latent_sizes<512, 64>(p, num_seqs, max_q_len, stream);
+  if (kv_rank == 64) code = launch_latent_sizes<64, 32>(p, num_seqs, max_q_len, two_blocks, stream);
+  else if (kv_rank == 128 && rot_dim == 32) code = launch_latent_sizes<128, 32>(p, num_seqs, max_q_len, two_blocks, stream);
+  else if (kv_rank == 128) code = launch_latent_sizes<128, 64>(p, num_seqs, max_q_len, two_blocks, stream);
+  else if (kv_rank == 256) code = launch_latent_sizes<256, 64>(p, num_seqs, max_q_len, two_blocks, stream);
+  else code = launch_latent_sizes<512, 64>(p, num_seqs, max_q_len, two_blocks, stream);
   if (code != 0 || p.num_splits <= 1) return code;
   return (int)launch_pdl(num_seqs, latent_merge_kernel, dim3(num_seqs, heads), dim3(128), 0, stream,
                          (const float*)partial_out, (const float*)partial_lse, seq_index, query_start_loc, (bf16*)out,

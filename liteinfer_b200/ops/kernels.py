@@ -108,7 +108,7 @@ _SIGNATURES = {
     "li_latent_attention_mma": ("attention_latent_mma", [
         c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-        c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+        c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "li_latent_attention_mma_supports": ("attention_latent_mma", [c_int, c_int, c_int]),
     "li_gate_heads": ("attention_latent", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1216,7 +1216,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
     if latent_mma_supports(q_raw.dtype, kv_rank, rot_dim, rot_dims):
         # Tensor cores: sequences that bring one token in a launch that splits their keys over blocks, the others
         # four queries a block; without a plan every sequence goes the second way.
-        def run(seq_index, count, q_len, splits=1):
+        def run(seq_index, count, q_len, splits=1, two_blocks=False):
             partial_out = partial_lse = None
             if splits > 1:
                 partial_out = torch.empty((splits, heads, tokens, kv_rank), dtype=torch.float32, device=out.device)
@@ -1226,7 +1226,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
                 q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
                 block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), _ptr(seq_index),
                 inv_freq.data_ptr(), _ptr(sink), count, q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages,
-                float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens,
+                float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens, int(two_blocks),
                 scratch_for(out.device).gemm_error.data_ptr(), _stream()),
                 "latent_attention_mma")
 
@@ -1238,10 +1238,12 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
         if plan.num_decode:
             chunks = -(-heads // 16)
             tiles = max(1, -(-plan.max_decode_context_len // 64))            # two tiles of 32 keys a split at least
-            # One block per SM (a block's two stages of entries fill most of its shared memory): as many splits
-            # as still make one wave.
-            splits = max(1, min(tiles, NUM_SMS // max(1, plan.num_decode * chunks), 32))
-            run(plan.decode_seqs, plan.num_decode, 1, splits)
+            # Two blocks of eight warps per SM where the batch is wide (measured at 16 heads over 2,048 keys: 67
+            # against 86 us at 64 sequences), one of sixteen where it is narrow (18.7 against 19.8 us at 8); as many
+            # splits as still make one wave of either.
+            two_blocks = plan.num_decode * chunks > 16
+            splits = max(1, min(tiles, (2 if two_blocks else 1) * NUM_SMS // max(1, plan.num_decode * chunks), 32))
+            run(plan.decode_seqs, plan.num_decode, 1, splits, two_blocks)
         return out
     _check(_fn("li_latent_attention")(
         _code(q_raw), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_raw.data_ptr(), q_raw.stride(0),

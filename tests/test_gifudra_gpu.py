@@ -185,7 +185,7 @@ def _attention_inputs(dtype, heads, c, r, d, query_lens, context_lens, page, pag
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,c,r,dims,d,page", [(3, 40, 10, 6, 12, 4), (1, 24, 2, 2, 5, 8), (6, 96, 32, 32, 16, 16),
-                                                   (16, 64, 32, 32, 32, 32), (9, 128, 64, 64, 8, 64), (2, 512, 64, 64, 4, 16)])
+                                                   (16, 64, 32, 32, 32, 32), (9, 128, 64, 64, 8, 64), (2, 512, 64, 64, 4, 16), (2, 640, 16, 16, 4, 16)])
 @pytest.mark.parametrize("sink", [True, False])
 def test_latent_attention_portions_and_single_tokens(dtype, heads, c, r, dims, d, page, sink):
     from liteinfer_b200 import ops
@@ -236,6 +236,26 @@ def test_latent_attention_on_tensor_cores_with_a_plan(heads, c, r, page, sink):
     unplanned = ops.latent_attention(*common, torch.zeros_like(q_lat), *rest)
     torch.testing.assert_close(planned.float(), want.float(), **_tol(dtype))
     torch.testing.assert_close(unplanned.float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("heads,c,r", [(16, 64, 32), (5, 512, 64), (20, 128, 32)])
+def test_latent_attention_wide_batch_of_single_tokens(heads, c, r):
+    """More than sixteen single-token sequences at once (the launch then runs two blocks per SM, rounds of 32 keys):
+    contexts of one token, on both sides of a round's and a stage's edge, and long enough for several splits."""
+    from liteinfer_b200 import ops
+
+    dtype, d, page = torch.bfloat16, 8, 16
+    context_lens = [1, 2, 31, 32, 33, 63, 64, 65, 96, 97, 100, 257, 500, 511, 512, 513, 700, 1000, 1024, 1500]
+    query_lens = [1] * len(context_lens)
+    pages = sum(-(-n // page) for n in context_lens) + 3
+    table, qsl, ctxl, pool, q_lat, q_raw = _attention_inputs(dtype, heads, c, r, d, query_lens, context_lens, page, pages, 3)
+    inv_freq = (1000.0 ** (-torch.arange(r // 2, dtype=torch.float64) * 2 / r)).float().to(DEV)
+    sinks = _randn(heads, seed=9)
+    common = (q_lat, q_raw, d + r, d)
+    rest = (pool, table, qsl, ctxl, inv_freq, sinks, len(context_lens), 1, heads, c, r, r, 0.09)
+    want = ref.latent_attention(*common, torch.empty_like(q_lat), *rest)
+    got = ops.latent_attention(*common, torch.zeros_like(q_lat), *rest, plan=_plan(query_lens, context_lens))
+    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype,c,r", [(torch.float32, 48, 8), (torch.bfloat16, 48, 8), (torch.bfloat16, 64, 32)])
