@@ -5,8 +5,8 @@
 // A block of sixteen (or eight) warps takes MT row tiles of 16 rows, a row tile being ONE query's heads h0..h0+15, and walks
 // the keys KT at a time (one bulk copy per entry into padded shared memory, a ring of stages behind mbarriers, the next
 // tiles on their way while this one is used).  Per tile of keys:
-//   1. scores: the MT x (KT / 8) units of 16 rows x 8 keys are dealt to the warps, one unit a warp, or two warps a
-//      unit, each then with a part of the (C + R) / 16 products and the halves added through shared memory; a
+//   1. scores: the units of 16 rows x 8 (or 16) keys are dealt to the warps, one unit a warp, or several warps a
+//      unit, each then with a part of the (C + R) / 16 products and the parts added through shared memory; a
 //      product is mma.sync m16n8k16 with the query rows (shared memory, ldmatrix) and the keys as they are stored
 //      ([key][number] is the product's column-major operand).  Scale, causal mask, the unit's row maxima.
 //   2. every row's new maximum from the units' maxima; probabilities, rounded to bfloat16, into shared memory;
@@ -59,11 +59,11 @@ constexpr int kPad = 8;         // bfloat16 of padding per shared-memory row: ro
 constexpr int kMaxStages = 6;
 
 // KT: keys of one stage (one ring slot); SUB: stages used per round of the loop (KI = SUB * KT keys); NS: slots.
-template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW, int UK>
 struct LatentSmem {
   static constexpr int KI = SUB * KT;
   static constexpr int D = C + R, LD = D + kPad, PLD = KI + kPad;
-  static constexpr int kRows = MT * 16, kUnits = MT * (KI / 8);
+  static constexpr int kRows = MT * 16, kUnits = MT * (KI / UK);      // UK: keys of a score unit, 8 or 16
   static constexpr size_t q_bytes = (size_t)kRows * LD * 2;
   static constexpr size_t k_bytes = (size_t)KT * LD * 2;
   static constexpr size_t p_bytes = (size_t)kRows * PLD * 2;
@@ -114,10 +114,12 @@ __device__ __forceinline__ void load_key_tile(bf16* ks, unsigned bar, const Late
   }
 }
 
-template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW, int UK>
 __global__ void __launch_bounds__(NW * 32, NW <= 8 ? 2 : 1)
 latent_attention_mma_kernel(const LatentParams p) {
-  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW>;
+  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW, UK>;
+  static_assert(UK == 8 || UK == 16, "a score unit is one or two tiles of 8 keys");
+  constexpr int kUnitTiles = UK / 8, kUnitsPerRow = S::KI / UK;
   constexpr int kLatentWarps = NW;
   constexpr int KI = S::KI;
   constexpr int D = S::D, LD = S::LD, PLD = S::PLD, kRows = S::kRows, kNTiles = KI / 8;
@@ -249,75 +251,113 @@ latent_attention_mma_kernel(const LatentParams p) {
     float* new_max = row_max + ((it + 1) & 1) * kRows;
     const int key0 = tile * KI;
 
-    // 1. scores: unit u = (row tile u / kNTiles, keys 8 * (u % kNTiles)...) belongs to warp u, or to warps u,
-    //    u + units, ..., which then take a part of the k-range each and add their parts through shared memory.
+    // 1. scores: unit u = (row tile u / units per row, UK keys from UK * (u % units per row) on) belongs to warp u,
+    //    or to warps u, u + units, ..., which then take a part of the k-range each and add their parts through
+    //    shared memory.  A unit of 16 keys uses every fragment of the query rows for two tiles of keys.
     const int u = warp % S::kUnits, khalf = warp / S::kUnits;
-    const int mt = u / kNTiles, nt = u % kNTiles;
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int mt = u / kUnitsPerRow, nt0 = (u % kUnitsPerRow) * kUnitTiles;     // its first tile of 8 keys
+    float sc[kUnitTiles][4];
+#pragma unroll
+    for (int j = 0; j < kUnitTiles; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
     {
       const bf16* qa = qs + (mt * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
-      const bf16* kb = ks0 + (size_t)((it * SUB + nt * 8 / KT) % NS) * KT * LD + (nt * 8 % KT + (lane & 7)) * LD + (lane >> 3) * 8;
+      const bf16* slot = ks0 + (size_t)((it * SUB + nt0 * 8 / KT) % NS) * KT * LD;
       const int k_begin = (khalf * kChunks32 / kSplitK) * 32, k_end = ((khalf + 1) * kChunks32 / kSplitK) * 32;
-      // Four partial sums, each over every fourth k-step: the products of one sum wait for each other, not for
-      // the other three's.
-      float part[3][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      if (UK == 8) {
+        const bf16* kb = slot + (nt0 * 8 % KT + (lane & 7)) * LD + (lane >> 3) * 8;
+        // Four partial sums, each over every fourth k-step: the products of one sum wait for each other, not for
+        // the other three's.
+        float part[3][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll 3
-      for (int k0 = k_begin; k0 < k_end; k0 += 64) {
-        unsigned a[4], a2[4], b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, kb + k0);          // keys nt*8.., numbers k0..k0+31: two k-steps
-        ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
-        ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
-        mma_bf16(sc, a, b0, b1);
-        mma_bf16(part[0], a2, b2, b3);
-        if (k0 + 32 < k_end) {
-          ldmatrix_x4(b0, b1, b2, b3, kb + k0 + 32);
-          ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0 + 32);
-          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 48);
-          mma_bf16(part[1], a, b0, b1);
-          mma_bf16(part[2], a2, b2, b3);
+        for (int k0 = k_begin; k0 < k_end; k0 += 64) {
+          unsigned a[4], a2[4], b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, kb + k0);          // keys nt0*8.., numbers k0..k0+31: two k-steps
+          ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
+          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
+          mma_bf16(sc[0], a, b0, b1);
+          mma_bf16(part[0], a2, b2, b3);
+          if (k0 + 32 < k_end) {
+            ldmatrix_x4(b0, b1, b2, b3, kb + k0 + 32);
+            ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0 + 32);
+            ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 48);
+            mma_bf16(part[1], a, b0, b1);
+            mma_bf16(part[2], a2, b2, b3);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[0][e] += part[0][e] + part[1][e] + part[2][e];
+      } else {
+        // 16 keys x 16 numbers per fetch: (keys 0-7 | 8-15) x (numbers 0-7 | 8-15); even and odd k-steps add into
+        // sums of their own, so four chains of products run side by side.
+        const bf16* kb = slot + (nt0 * 8 % KT + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
+        float part[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+        for (int k0 = k_begin; k0 < k_end; k0 += 32) {
+          unsigned a[4], a2[4], b0, b1, b2, b3, c0, c1, c2, c3;
+          ldmatrix_x4(a[0], a[1], a[2], a[3], qa + k0);
+          ldmatrix_x4(b0, b1, b2, b3, kb + k0);
+          ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + k0 + 16);
+          ldmatrix_x4(c0, c1, c2, c3, kb + k0 + 16);
+          mma_bf16(sc[0], a, b0, b1);
+          mma_bf16(sc[kUnitTiles - 1], a, b2, b3);
+          mma_bf16(part[0], a2, c0, c1);
+          mma_bf16(part[1], a2, c2, c3);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          sc[0][e] += part[0][e];
+          sc[kUnitTiles - 1][e] += part[1][e];
         }
       }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sc[e] += part[0][e] + part[1][e] + part[2][e];
     }
     if (kSplitK > 1) {
-      float* lo = half_scores + (mt * 16 + g) * KI + nt * 8 + 2 * t4;
+      float* lo = half_scores + (mt * 16 + g) * KI + nt0 * 8 + 2 * t4;
       if (khalf > 0) {
-        *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI) = make_float2(sc[0], sc[1]);
-        *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI + 8 * KI) = make_float2(sc[2], sc[3]);
+#pragma unroll
+        for (int j = 0; j < kUnitTiles; ++j) {
+          *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI + 8 * j) = make_float2(sc[j][0], sc[j][1]);
+          *reinterpret_cast<float2*>(lo + (khalf - 1) * kRows * KI + 8 * KI + 8 * j) = make_float2(sc[j][2], sc[j][3]);
+        }
       }
       __syncthreads();
       if (khalf == 0) {
 #pragma unroll
         for (int part = 0; part < kSplitK - 1; ++part) {
-          const float2 x = *reinterpret_cast<const float2*>(lo + part * kRows * KI);
-          const float2 y = *reinterpret_cast<const float2*>(lo + part * kRows * KI + 8 * KI);
-          sc[0] += x.x; sc[1] += x.y; sc[2] += y.x; sc[3] += y.y;
+#pragma unroll
+          for (int j = 0; j < kUnitTiles; ++j) {
+            const float2 x = *reinterpret_cast<const float2*>(lo + part * kRows * KI + 8 * j);
+            const float2 y = *reinterpret_cast<const float2*>(lo + part * kRows * KI + 8 * KI + 8 * j);
+            sc[j][0] += x.x; sc[j][1] += x.y; sc[j][2] += y.x; sc[j][3] += y.y;
+          }
         }
       }
     }
     if (khalf == 0) {
-      // Scale, mask (key j is visible to the query at position pos iff j <= pos), and the unit's row maxima.
+      // Scale, mask (key j is visible to the query at position pos iff j <= pos), and the row maxima per tile of 8 keys.
       const int pos = first_pos + mt;
-      const int kcol = key0 + nt * 8 + 2 * t4;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = kcol + (e & 1);
-        sc[e] = key <= pos ? sc[e] * p.scale_log2 : -INFINITY;
-      }
-      float m_lo = fmaxf(sc[0], sc[1]), m_hi = fmaxf(sc[2], sc[3]);
-      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
-      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
-      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
-      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
-      if (t4 == 0) {
-        unit_max[nt * kRows + mt * 16 + g] = m_lo;
-        unit_max[nt * kRows + mt * 16 + g + 8] = m_hi;
+      for (int j = 0; j < kUnitTiles; ++j) {
+        const int nt = nt0 + j;
+        const int kcol = key0 + nt * 8 + 2 * t4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kcol + (e & 1);
+          sc[j][e] = key <= pos ? sc[j][e] * p.scale_log2 : -INFINITY;
+        }
+        float m_lo = fmaxf(sc[j][0], sc[j][1]), m_hi = fmaxf(sc[j][2], sc[j][3]);
+        m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+        m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
+        m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+        m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
+        if (t4 == 0) {
+          unit_max[nt * kRows + mt * 16 + g] = m_lo;
+          unit_max[nt * kRows + mt * 16 + g + 8] = m_hi;
+        }
       }
     }
     __syncthreads();
 
-    // 2. the rows' new maxima (their own threads store them), probabilities into shared memory, the units' sums.
+    // 2. the rows' new maxima (their own threads store them), probabilities into shared memory, the tiles' sums.
     if (threadIdx.x < kRows) {
       float m = old_max[threadIdx.x];
 #pragma unroll
@@ -332,20 +372,24 @@ latent_attention_mma_kernel(const LatentParams p) {
         m_lo = fmaxf(m_lo, unit_max[n * kRows + r_lo]);
         m_hi = fmaxf(m_hi, unit_max[n * kRows + r_hi]);
       }
-      const float p0 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[0] - m_lo);
-      const float p1 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[1] - m_lo);
-      const float p2 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[2] - m_hi);
-      const float p3 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[3] - m_hi);
-      *reinterpret_cast<__nv_bfloat162*>(ps + r_lo * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p0, p1);
-      *reinterpret_cast<__nv_bfloat162*>(ps + r_hi * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p2, p3);
-      float s_lo = p0 + p1, s_hi = p2 + p3;
-      s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1);
-      s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
-      s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1);
-      s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
-      if (t4 == 0) {
-        unit_sum[nt * kRows + r_lo] = s_lo;
-        unit_sum[nt * kRows + r_hi] = s_hi;
+#pragma unroll
+      for (int j = 0; j < kUnitTiles; ++j) {
+        const int nt = nt0 + j;
+        const float p0 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[j][0] - m_lo);
+        const float p1 = m_lo == -INFINITY ? 0.f : fast_exp2(sc[j][1] - m_lo);
+        const float p2 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[j][2] - m_hi);
+        const float p3 = m_hi == -INFINITY ? 0.f : fast_exp2(sc[j][3] - m_hi);
+        *reinterpret_cast<__nv_bfloat162*>(ps + r_lo * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p0, p1);
+        *reinterpret_cast<__nv_bfloat162*>(ps + r_hi * PLD + nt * 8 + 2 * t4) = __floats2bfloat162_rn(p2, p3);
+        float s_lo = p0 + p1, s_hi = p2 + p3;
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1);
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+        s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1);
+        s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+        if (t4 == 0) {
+          unit_sum[nt * kRows + r_lo] = s_lo;
+          unit_sum[nt * kRows + r_hi] = s_hi;
+        }
       }
     }
     __syncthreads();
@@ -359,33 +403,39 @@ latent_attention_mma_kernel(const LatentParams p) {
       const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_old - m_new);
       row_sum[threadIdx.x] = row_sum[threadIdx.x] * alpha + s;
     }
+    if (warp < kOwnWarps) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      if (warp >= kOwnWarps) break;
-      const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
-      const float n_lo = new_max[r_lo], n_hi = new_max[r_hi];
-      const float a_lo = n_lo == -INFINITY ? 1.f : fast_exp2(old_max[r_lo] - n_lo);
-      const float a_hi = n_hi == -INFINITY ? 1.f : fast_exp2(old_max[r_hi] - n_hi);
-      if (a_lo != 1.f || a_hi != 1.f) {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+        const float n_lo = new_max[r_lo], n_hi = new_max[r_hi];
+        const float a_lo = n_lo == -INFINITY ? 1.f : fast_exp2(old_max[r_lo] - n_lo);
+        const float a_hi = n_hi == -INFINITY ? 1.f : fast_exp2(old_max[r_hi] - n_hi);
+        if (a_lo != 1.f || a_hi != 1.f) {
 #pragma unroll
-        for (int n = 0; n < kOwnTiles; ++n) {
-          acc[mt][n][0] *= a_lo; acc[mt][n][1] *= a_lo;
-          acc[mt][n][2] *= a_hi; acc[mt][n][3] *= a_hi;
+          for (int n = 0; n < kOwnTiles; ++n) {
+            acc[mt][n][0] *= a_lo; acc[mt][n][1] *= a_lo;
+            acc[mt][n][2] *= a_hi; acc[mt][n][3] *= a_hi;
+          }
         }
       }
-      const bf16* pa = ps + (mt * 16 + (lane & 15)) * PLD + (lane >> 4) * 8;
+      // The entries' fragments are fetched once per 16 keys and serve every row tile.
 #pragma unroll
       for (int k0 = 0; k0 < KI; k0 += 16) {
-        unsigned a[4];
-        ldmatrix_x4(a[0], a[1], a[2], a[3], pa + k0);
         const bf16* vb = ks0 + (size_t)((it * SUB + k0 / KT) % NS) * KT * LD +
                          (k0 % KT + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + warp * kOwn + (lane >> 4) * 8;
+        unsigned vf[(kOwnTiles + 1) / 2][4];
 #pragma unroll
-        for (int n = 0; n < kOwnTiles; n += 2) {
-          unsigned b0, b1, b2, b3;
-          ldmatrix_x4_trans(b0, b1, b2, b3, vb + n * 8);      // keys k0..k0+15, numbers of two 8-wide tiles
-          mma_bf16(acc[mt][n], a, b0, b1);
-          if (n + 1 < kOwnTiles) mma_bf16(acc[mt][n + 1], a, b2, b3);
+        for (int n = 0; n < kOwnTiles; n += 2)
+          ldmatrix_x4_trans(vf[n / 2][0], vf[n / 2][1], vf[n / 2][2], vf[n / 2][3], vb + n * 8);   // two 8-wide tiles
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          unsigned a[4];
+          ldmatrix_x4(a[0], a[1], a[2], a[3], ps + (mt * 16 + (lane & 15)) * PLD + (lane >> 4) * 8 + k0);
+#pragma unroll
+          for (int n = 0; n < kOwnTiles; n += 2) {
+            mma_bf16(acc[mt][n], a, vf[n / 2][0], vf[n / 2][1]);
+            if (n + 1 < kOwnTiles) mma_bf16(acc[mt][n + 1], a, vf[n / 2][2], vf[n / 2][3]);
+          }
         }
       }
     }
@@ -483,18 +533,18 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const
   }
 }
 
-template <int C, int R, int MT, int KT, int SUB, int NS, int NW>
+template <int C, int R, int MT, int KT, int SUB, int NS, int NW, int UK>
 int launch_latent(const LatentParams& p, int num_seqs, int row_tiles, cudaStream_t stream) {
-  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW>;
+  using S = LatentSmem<C, R, MT, KT, SUB, NS, NW, UK>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW>,
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW, UK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::total);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(row_tiles * (p.num_splits > 1 ? p.num_splits : 1), (p.heads + 15) / 16, num_seqs);
-  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW>, grid, dim3(NW * 32),
+  return (int)launch_pdl(row_tiles * MT, latent_attention_mma_kernel<C, R, MT, KT, SUB, NS, NW, UK>, grid, dim3(NW * 32),
                          S::total, stream, p);
 }
 
@@ -505,10 +555,10 @@ int launch_latent_sizes(const LatentParams& p, int num_seqs, int max_q_len, int 
     // Two blocks of eight warps per SM (rounds of 32 keys, two stages each): while one block stands at a barrier
     // the other works.  Or one block of sixteen warps (rounds of 64 keys from five stages of 32): fewer, longer
     // blocks, which a narrow batch with many splits does a little better with.
-    if (two_blocks) return launch_latent<C, R, 1, 32, 1, 2, 8>(p, num_seqs, 1, stream);
-    return launch_latent<C, R, 1, 32, 2, 5, 16>(p, num_seqs, 1, stream);
+    if (two_blocks) return launch_latent<C, R, 1, 32, 1, 2, 8, 8>(p, num_seqs, 1, stream);
+    return launch_latent<C, R, 1, 32, 2, 5, 16, 8>(p, num_seqs, 1, stream);
   }
-  return launch_latent<C, R, 4, 32, 1, 3, 16>(p, num_seqs, (max_q_len + 3) / 4, stream);
+  return launch_latent<C, R, 4, 32, 1, 3, 16, 16>(p, num_seqs, (max_q_len + 3) / 4, stream);
 }
 
 }  // namespace li
