@@ -229,15 +229,6 @@ latent_attention_mma_kernel(const LatentParams p) {
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int it = tile - tile_begin;
-    if (warp == 0 && it > 0) {          // the slots that the round before this one used are free: fill them again
-#pragma unroll
-      for (int j = 0; j < SUB; ++j) {
-        const int r = (it - 1) * SUB + j + NS;
-        if (r < stages_total)
-          load_key_tile<C, R, KT>(ks0 + (size_t)(r % NS) * KT * LD, bars + 8 * (r % NS), p, table, table_cache, cached_first,
-                                  cached_count, (tile_begin * SUB + r) * KT, last_pos + 1);
-      }
-    }
     // This tile's entries have landed when its stage's barrier has turned (the next one's may be on their way).  A
     // wait that runs out raises the error flag; the block then stops, all of its threads together.
     bool landed = true;
@@ -247,6 +238,16 @@ latent_attention_mma_kernel(const LatentParams p) {
       landed = mbar_wait(bars + 8 * (r % NS), (unsigned)(r / NS) & 1, p.error_flag, 31) && landed;
     }
     if (__syncthreads_or(!landed)) break;
+    // Every warp is past the round before this one (its probabilities and its stages may be overwritten).
+    if (warp == 0 && it > 0) {          // the slots that the round before this one used are free: fill them again
+#pragma unroll
+      for (int j = 0; j < SUB; ++j) {
+        const int r = (it - 1) * SUB + j + NS;
+        if (r < stages_total)
+          load_key_tile<C, R, KT>(ks0 + (size_t)(r % NS) * KT * LD, bars + 8 * (r % NS), p, table, table_cache, cached_first,
+                                  cached_count, (tile_begin * SUB + r) * KT, last_pos + 1);
+      }
+    }
     const float* old_max = row_max + (it & 1) * kRows;
     float* new_max = row_max + ((it + 1) & 1) * kRows;
     const int key0 = tile * KI;
@@ -439,8 +440,8 @@ latent_attention_mma_kernel(const LatentParams p) {
         }
       }
     }
-    __syncthreads();      // the probabilities and this stage of entries may be overwritten
   }
+  __syncthreads();
   // The end: denominators (with the sink's term where this block sees all keys), then the rows leave.
   const int final_buf = ((tile_end > tile_begin ? tile_end - tile_begin : 0) & 1) * kRows;   // where the last tile left the maxima
   if (threadIdx.x < kRows) {
