@@ -509,7 +509,8 @@ def _gifudra_kernels(peaks: dict) -> dict:
     q_lat, q_raw = (torch.randn(H, n, C, device=dev) * 0.3).to(bf), torch.randn(n, H * (dm + R), device=dev).to(bf)
     o_lat = torch.empty_like(q_lat)
     plan = AttentionPlan(num_prefill=1, prefill_seqs=ints([0]), max_prefill_query_len=n)
-    ms = _timed(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, ints([0, n]), ints([n]), inv_freq,
+    qsl, ctxl = ints([0, n]), ints([n])
+    ms = _timed(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, qsl, ctxl, inv_freq,
                                              sink, 1, n, H, C, R, R, 0.07, plan=plan))
     out["latent_attention_prompt_us"] = ms * 1e3
     out["latent_attention_prompt_tflops_frac"] = 2 * H * (2 * C + R) * n * (n + 1) / 2 / (ms * 1e-3) / tflops

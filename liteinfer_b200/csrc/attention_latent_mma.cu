@@ -499,14 +499,16 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const
                                     int out_token_stride, const float* __restrict__ sink, int heads, int tokens,
                                     int C, int num_splits) {
   __shared__ float weight[kMaxSplits];
-  grid_dependency_wait();
-  grid_launch_dependents();
+  // What the step itself brings (the sequence list, the tokens' places, the sinks) is read while the kernel ahead
+  // still runs; its partial results only behind the wait.
   const int seq = seq_index ? seq_index[blockIdx.x] : blockIdx.x;
   const int head = blockIdx.y;
+  const int token = seq < 0 ? 0 : query_start_loc[seq];         // the sequence's one token
+  const float sk = sink ? sink[head] * kLog2e : -INFINITY;
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (seq < 0) return;                            // a place of padding
-  const int token = query_start_loc[seq];         // the sequence's one token
   if (threadIdx.x < 32) {
-    const float sk = sink ? sink[head] * kLog2e : -INFINITY;
     const float lse = (int)threadIdx.x < num_splits
                           ? partial_lse[((size_t)threadIdx.x * heads + head) * tokens + token] : -INFINITY;
     float m = fmaxf(lse, sk);
