@@ -74,44 +74,42 @@ struct LatentSmem {
   static constexpr size_t total = q_bytes + NS * k_bytes + p_bytes + (f_floats + s_floats) * 4;
 };
 
-// Called by warp 0: every lane looks its keys up in the block table once; lane 0 tells the stage's mbarrier how
-// many bytes to expect, then every visible entry is ONE bulk copy (no thread computes an address per 16 bytes).
-// An entry that is not visible (behind the last query, or on a page given back) is written as zeros.
-template <int C, int R, int KT>
+// Called by every warp: warp w brings keys [w * KT / NW, (w + 1) * KT / NW) of the stage, one lane a key.  The
+// lane looks its key up in the block table; the warp's first lane arrives at the stage's mbarrier (which counts NW
+// arrivals) and tells it how many bytes the warp's copies bring; then every visible entry is ONE bulk copy (no
+// thread computes an address per 16 bytes, and no warp issues more than its share of the copies).  An entry that
+// is not visible (behind the last query, or on a page given back) is written as zeros.
+template <int C, int R, int KT, int NW>
 __device__ __forceinline__ void load_key_tile(bf16* ks, unsigned bar, const LatentParams& p, const int* table,
                                               const int* cached, int cached_first, int cached_count, int key0,
                                               int limit) {
   constexpr int D = C + R, LD = D + kPad;
   constexpr unsigned kRowBytes = D * 2;
-  const int lane = threadIdx.x & 31;
-  const bf16* src[KT / 32];
-  int count = 0;
-#pragma unroll
-  for (int j = 0; j < KT / 32; ++j) {
-    const int kpos = key0 + lane + 32 * j;
-    src[j] = nullptr;
+  constexpr int kPerWarp = KT / NW;
+  static_assert(kPerWarp * NW == KT && kPerWarp >= 1 && kPerWarp <= 32, "the keys of a stage are dealt to the warps evenly");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = warp * kPerWarp + lane;            // the lane's key within the stage
+  const bf16* src = nullptr;
+  if (lane < kPerWarp) {
+    const int kpos = key0 + row;
     if (kpos < limit) {
       // The block's part of the block table lies in shared memory (its first `cached_count` entries from
       // `cached_first` on); a look-up there does not hold the copies up for a trip to memory.
       const int block = kpos / p.page_size, at = block - cached_first;
       const int page = at < cached_count ? cached[at] : table[block];
-      if (page >= 0 && page < p.num_pages) src[j] = p.pool + ((size_t)page * p.page_size + kpos % p.page_size) * D;
+      if (page >= 0 && page < p.num_pages) src = p.pool + ((size_t)page * p.page_size + kpos % p.page_size) * D;
     }
-    count += src[j] != nullptr;
   }
-  count = __reduce_add_sync(0xffffffffu, count);
-  if (lane == 0) mbar_expect_tx(bar, (unsigned)count * kRowBytes);
+  const int count = __reduce_add_sync(0xffffffffu, src != nullptr ? 1 : 0);
+  if (lane < kPerWarp && !src) {
+    bf16* dst = ks + row * LD;
+    for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+    fence_async_shared();       // a later bulk copy into this row comes behind these stores
+  }
   __syncwarp();
-#pragma unroll
-  for (int j = 0; j < KT / 32; ++j) {
-    bf16* dst = ks + (lane + 32 * j) * LD;
-    if (src[j]) {
-      bulk_load(smem_addr(dst), src[j], kRowBytes, bar);
-    } else {
-      for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
-      fence_async_shared();       // a later bulk copy into this row comes behind these stores
-    }
-  }
+  if (lane == 0) mbar_expect_tx(bar, (unsigned)count * kRowBytes);      // the warp's arrival, and its bytes
+  __syncwarp();
+  if (src) bulk_load(smem_addr(ks + row * LD), src, kRowBytes, bar);
 }
 
 template <int C, int R, int MT, int KT, int SUB, int NS, int NW, int UK>
@@ -162,7 +160,7 @@ latent_attention_mma_kernel(const LatentParams p) {
 
   const unsigned bars = smem_addr(stage_bars);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NS; ++i) mbar_init(bars + 8 * i, 1);
+    for (int i = 0; i < NS; ++i) mbar_init(bars + 8 * i, NW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -176,11 +174,9 @@ latent_attention_mma_kernel(const LatentParams p) {
   // turns that slot's barrier for the (r / NS)-th time.  A stage behind the last key is still "loaded": its rows are
   // written as zeros and its barrier turns, so the loop needs no special case for it.
   const int stages_total = (tile_end - tile_begin) * SUB;
-  if (warp == 0) {             // every slot filled before the first round
-    for (int r = 0; r < NS && r < stages_total; ++r)
-      load_key_tile<C, R, KT>(ks0 + (size_t)r * KT * LD, bars + 8 * r, p, table, table_cache, cached_first, cached_count,
-                              (tile_begin * SUB + r) * KT, last_pos + 1);
-  }
+  for (int r = 0; r < NS && r < stages_total; ++r)      // every slot filled before the first round
+    load_key_tile<C, R, KT, NW>(ks0 + (size_t)r * KT * LD, bars + 8 * r, p, table, table_cache, cached_first, cached_count,
+                                (tile_begin * SUB + r) * KT, last_pos + 1);
 
   // The query rows: row 16 * i + j is head head0 + j of query query0 + i; [absorbed query | rotated part].
   for (int i = threadIdx.x; i < kRows * (C / 8); i += kLatentWarps * 32) {
@@ -239,13 +235,13 @@ latent_attention_mma_kernel(const LatentParams p) {
     }
     if (__syncthreads_or(!landed)) break;
     // Every warp is past the round before this one (its probabilities and its stages may be overwritten).
-    if (warp == 0 && it > 0) {          // the slots that the round before this one used are free: fill them again
+    if (it > 0) {          // the slots that the round before this one used are free: fill them again
 #pragma unroll
       for (int j = 0; j < SUB; ++j) {
         const int r = (it - 1) * SUB + j + NS;
         if (r < stages_total)
-          load_key_tile<C, R, KT>(ks0 + (size_t)(r % NS) * KT * LD, bars + 8 * (r % NS), p, table, table_cache, cached_first,
-                                  cached_count, (tile_begin * SUB + r) * KT, last_pos + 1);
+          load_key_tile<C, R, KT, NW>(ks0 + (size_t)(r % NS) * KT * LD, bars + 8 * (r % NS), p, table, table_cache,
+                                      cached_first, cached_count, (tile_begin * SUB + r) * KT, last_pos + 1);
       }
     }
     const float* old_max = row_max + (it & 1) * kRows;
