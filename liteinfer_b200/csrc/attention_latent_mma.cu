@@ -487,8 +487,10 @@ latent_attention_mma_kernel(const LatentParams p) {
 }
 
 // The splits of a (token, head) row merged: out = sum_s w_s O_s / (sum_s w_s + the sink's term), w_s = 2^(lse_s - max).
-// The weights are worked out once per block; a thread then adds up its numbers with all loads on their way at once.
+// The weights are worked out once per block; a thread adds up its numbers kBatch splits at a time, all their loads
+// on their way at once.
 constexpr int kMaxSplits = 32;
+template <int kBatch>      // partial rows a thread has on their way at once: few for few splits (fewer registers)
 __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
                                     const int* __restrict__ seq_index, const int* __restrict__ query_start_loc,
                                     bf16* __restrict__ out, long out_head_stride,
@@ -504,6 +506,17 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const
   grid_dependency_wait();
   grid_launch_dependents();
   if (seq < 0) return;                            // a place of padding
+  // A thread's first partial rows are on their way while the first warp works out the weights.
+  float4 x[kBatch];
+  const int d0 = threadIdx.x * 4;
+  auto part = [&](int s, int d) {
+    return *reinterpret_cast<const float4*>(partial_out + (((size_t)s * heads + head) * tokens + token) * C + d);
+  };
+  if (d0 < C) {
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (j < num_splits) x[j] = part(j, d0);
+  }
   if (threadIdx.x < 32) {
     const float lse = (int)threadIdx.x < num_splits
                           ? partial_lse[((size_t)threadIdx.x * heads + head) * tokens + token] : -INFINITY;
@@ -518,13 +531,21 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial_out, const
     weight[threadIdx.x] = denom > 0.f ? w / denom : 0.f;
   }
   __syncthreads();
-  for (int d = threadIdx.x * 4; d < C; d += blockDim.x * 4) {
+  for (int d = d0; d < C; d += blockDim.x * 4) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int s = 0; s < num_splits; ++s) {
-      const float w = weight[s];
-      const float4 x = *reinterpret_cast<const float4*>(partial_out + (((size_t)s * heads + head) * tokens + token) * C + d);
-      v.x = fmaf(w, x.x, v.x); v.y = fmaf(w, x.y, v.y); v.z = fmaf(w, x.z, v.z); v.w = fmaf(w, x.w, v.w);
+    for (int base = 0; base < num_splits; base += kBatch) {
+      if (d != d0 || base != 0) {
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j)
+          if (base + j < num_splits) x[j] = part(base + j, d);
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (base + j < num_splits) {
+          const float w = weight[base + j];
+          v.x = fmaf(w, x[j].x, v.x); v.y = fmaf(w, x[j].y, v.y); v.z = fmaf(w, x[j].z, v.z); v.w = fmaf(w, x[j].w, v.w);
+        }
+      }
     }
     bf16* o = out + (size_t)head * out_head_stride + (size_t)token * out_token_stride + d;
     *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v.x, v.y);
@@ -609,7 +630,8 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
   else if (kv_rank == 256) code = launch_latent_sizes<256, 64>(p, num_seqs, max_q_len, two_blocks, stream);
   else code = launch_latent_sizes<512, 64>(p, num_seqs, max_q_len, two_blocks, stream);
   if (code != 0 || p.num_splits <= 1) return code;
-  return (int)launch_pdl(num_seqs, latent_merge_kernel, dim3(num_seqs, heads), dim3(128), 0, stream,
-                         (const float*)partial_out, (const float*)partial_lse, seq_index, query_start_loc, (bf16*)out,
-                         out_head_stride, out_token_stride, sink, heads, tokens, kv_rank, p.num_splits);
+  return (int)launch_pdl(num_seqs, p.num_splits <= 4 ? latent_merge_kernel<4> : latent_merge_kernel<16>, dim3(num_seqs, heads),
+                         dim3(128), 0, stream, (const float*)partial_out, (const float*)partial_lse, seq_index,
+                         query_start_loc, (bf16*)out, out_head_stride, out_token_stride, sink, heads, tokens, kv_rank,
+                         p.num_splits);
 }
