@@ -46,7 +46,8 @@ LI_EXPORT int li_gemm_skinny_plan(int N, int K, int* warps, int* slice_k) { retu
 // bfloat16 only; 1 <= M <= 64; K a multiple of 8 and 16-byte aligned rows.  scratch (float) and counters
 // (unsigned, all zero) are needed when li_gemm_skinny_plan(N, K) > 1: scratch_floats must be at least
 // tiles * slices * 16 * 8 * ceil(M/8) and num_counters at least tiles, with tiles = ceil(N/16).
-// gated_act: -1 plain; 0 silu, 1 gelu, 2 gelu-tanh, 3 relu on rows interleaved in eights (N a multiple of 16);
+// gated_act: -1 plain; 16 + a: plain, then the activation a of one argument (4: the square of relu);
+// 0 silu, 1 gelu, 2 gelu-tanh, 3 relu on rows interleaved in eights (N a multiple of 16);
 // out is then [M, N/2].
 static int run_skinny(SkinnyParams p, float* scratch, size_t scratch_floats, unsigned* counters, int num_counters,
                       cudaStream_t stream) {
@@ -88,7 +89,7 @@ LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, voi
                              int num_counters, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
-  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (!act_code_known(gated_act) || (!act_is_plain(gated_act) && (N % 16))) return LI_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
   SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
                  scratch, counters};
@@ -108,7 +109,7 @@ LI_EXPORT int li_gemm_skinny_fused(const void* x, const void* w, const void* bia
                                    cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
-  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (!act_code_known(gated_act) || (!act_is_plain(gated_act) && (N % 16))) return LI_ERR_UNSUPPORTED;
   if (out_sumsq && (gated_act >= 0 || out_stride < M)) return LI_ERR_UNSUPPORTED;
   if (norm_weight && (!in_sumsq || in_parts < 1)) return LI_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w) || (norm_weight && !aligned16(norm_weight))) return LI_ERR_ALIGNMENT;

@@ -44,6 +44,24 @@ __device__ __forceinline__ float gated(float gate, float up, int act) {
   return __bfloat162float(__float2bfloat16_rn(a)) * up;   // the activation is rounded before the multiply
 }
 
+// `gated_act` values from kUnaryActBase on ask for a plain product whose result, rounded to bfloat16 as a separate
+// kernel would see it, goes through an activation of one argument: base + 0 silu, 1 gelu, 2 gelu-tanh, 3 relu,
+// 4 the square of relu.
+constexpr int kUnaryActBase = 16, kUnaryActLast = 20;
+__device__ __forceinline__ float unary_act(float v, int act) {
+  v = __bfloat162float(__float2bfloat16_rn(v));
+  switch (act) {
+    case 0: return v / (1.0f + expf(-v));
+    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
+    case 4: { const float r = fmaxf(v, 0.f); return r * r; }
+    default: return fmaxf(v, 0.f);
+  }
+}
+// Whether a `gated_act` is one the kernels know, and whether it leaves the output as wide as the weight has rows.
+inline bool act_code_known(int gated_act) { return gated_act <= 3 || (gated_act >= kUnaryActBase && gated_act <= kUnaryActLast); }
+__host__ __device__ __forceinline__ bool act_is_plain(int gated_act) { return gated_act < 0 || gated_act >= kUnaryActBase; }
+
 struct SkinnyParams {
   const bf16* x;
   const bf16* w;
@@ -269,7 +287,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
       if (r == 0 && m < M) p.out_sumsq[(size_t)tile * p.out_stride + m] = sq;
     }
-  } else if (p.gated_act < 0) {
+  } else if (act_is_plain(p.gated_act)) {
     for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) {
       const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
       const int n = row0 + r;
@@ -277,6 +295,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       float sum = partial[0][r][m];
       if (kNorm) sum *= inv_rms[m];
       if (p.bias) sum += __bfloat162float(p.bias[n]);
+      if (p.gated_act >= kUnaryActBase) sum = unary_act(sum, p.gated_act - kUnaryActBase);
       p.out[(size_t)m * N + n] = __float2bfloat16_rn(sum);
     }
   } else {

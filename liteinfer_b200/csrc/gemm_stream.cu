@@ -39,7 +39,7 @@ struct StreamParams {
   const bf16* bias;
   bf16* out;
   int M, N, K;
-  int gated_act;      // -1: plain product
+  int gated_act;      // -1: plain product; from kUnaryActBase on: plain, then an activation of one argument
   float* out_sumsq;   // not null: out is added to, and [tiles][out_stride] receives the new rows' sums of squares
   int out_stride;
   int* error_flag;
@@ -57,7 +57,7 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
 template <int kCols, typename Sum>
 __device__ __forceinline__ void finish_tile(const StreamParams& p, int tile, int first, int step, Sum sum) {
   const int M = p.M, N = p.N, row0 = tile * 16;
-  if (p.gated_act < 0) {
+  if (act_is_plain(p.gated_act)) {
     for (int e = first; e < 16 * kCols; e += step) {
       const int r = e % 16, m = e / 16;
       const int col = row0 + r;
@@ -76,6 +76,7 @@ __device__ __forceinline__ void finish_tile(const StreamParams& p, int tile, int
         for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         if (r == 0 && m < M) p.out_sumsq[(size_t)tile * p.out_stride + m] = sq;
       } else if (live) {
+        if (p.gated_act >= kUnaryActBase) v = unary_act(v, p.gated_act - kUnaryActBase);
         p.out[(size_t)m * N + col] = __float2bfloat16_rn(v);
       }
     }
@@ -376,7 +377,7 @@ LI_EXPORT int li_gemm_stream(const void* x, const void* w, const void* bias, voi
                              int gated_act, float* out_sumsq, int out_stride, int* error_flag, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (!li_gemm_stream_supports(M, N, K)) return LI_ERR_UNSUPPORTED;
-  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (!act_code_known(gated_act) || (!act_is_plain(gated_act) && (N % 16))) return LI_ERR_UNSUPPORTED;
   if (out_sumsq && (gated_act >= 0 || out_stride < M)) return LI_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
   CUtensorMap map;

@@ -24,6 +24,8 @@ _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "gelu_tanh": 2, "relu": 3}
 # Activations of a feed-forward without a gate (`activation`): the above, and the square of relu.
 UNARY_ACTIVATIONS = {**ACTIVATIONS, "relu_squared": 4}
+# A weight-streaming product takes an activation of one argument as this base plus its code (csrc/gemm_skinny.cuh).
+UNARY_ACT_BASE = 16
 
 _ERRORS = {
     100001: "the kernel refuses these sizes (unsupported shape or option)",
@@ -403,7 +405,8 @@ def _streams(M: int, N: int, K: int) -> bool:
 
 
 def linear(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, out: torch.Tensor | None,
-           bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> "torch.Tensor | RowStats":
+           bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+           activation: str | None = None) -> "torch.Tensor | RowStats":
     """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias).
 
     float32 runs the FFMA kernel (a true 32-bit product: tensor cores have no such
@@ -415,7 +418,15 @@ def linear(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, out: torch.Ten
     the norm first.  With `residual` [M, N] the weight-streaming kernel adds its result into it
     (residual = round(residual + round(product))) and returns the new rows' `RowStats`, `out` being unused; any
     other path returns the product in `out`, for the caller to add.
+
+    `activation` (a name of `UNARY_ACTIVATIONS`; not with `residual`): out = act(product), the product rounded to
+    the engine's dtype first; the weight-streaming kernel does it on its way out, any other path by the
+    elementwise kernel.
     """
+    if activation is not None:
+        assert residual is None
+        if activation not in UNARY_ACTIVATIONS:
+            raise KernelLibraryError(f"activation {activation!r} has no kernel; known: {sorted(UNARY_ACTIVATIONS)}")
     pending = x if isinstance(x, PendingNorm) else None
     M, K = x.shape
     N = weight.shape[0]
@@ -433,13 +444,16 @@ def linear(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, out: torch.Ten
     if x.dtype == torch.float32:
         _check(_fn("li_gemm_simt")(0, x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
                                    _stream()), "gemm_simt")
-        return out
+        return out if activation is None else _unary(out, out, activation)
     if fused:
-        return _skinny(x, weight, out, bias, -1, residual)
+        return _skinny(x, weight, out, bias, -1 if activation is None else UNARY_ACT_BASE + UNARY_ACTIVATIONS[activation],
+                       residual)
     if M > 0:
         torch.mm(x, weight.t(), out=out)
         if bias is not None:
             add_bias_(out, bias)
+        if activation is not None:
+            _unary(out, out, activation)
     return out
 
 
@@ -1146,6 +1160,9 @@ def activation(x: torch.Tensor, out: torch.Tensor, name: str) -> torch.Tensor:
     _check(_fn("li_activation")(_code(x), x.data_ptr(), out.data_ptr(), x.numel(), UNARY_ACTIVATIONS[name], _stream()),
            "activation")
     return out
+
+
+_unary = activation      # for callers whose own `activation` argument hides the function's name
 
 
 def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

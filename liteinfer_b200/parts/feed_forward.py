@@ -94,8 +94,7 @@ class DenseMLP:
         self.up_weight, self.down_weight = tensors["up_proj.weight"], tensors["down_proj.weight"]
 
     def forward(self, x, ctx: StepContext):
-        hidden = ops.linear(x, self.up_weight, None)
-        ops.activation(hidden, hidden, self.activation)
+        hidden = ops.linear(x, self.up_weight, None, activation=self.activation)      # one kernel for a few rows of x
         return ops.linear(hidden, self.down_weight, None)
 
 

@@ -114,6 +114,25 @@ def test_squared_relu_and_gate(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 264, 96), (5, 4096, 512), (8, 200, 1024), (12, 328, 96), (16, 8192, 256), (40, 264, 96)])
+@pytest.mark.parametrize("name", ["relu_squared", "silu", "gelu_tanh"])
+def test_linear_with_activation(dtype, M, N, K, name):
+    """The product with the activation on its way out (a few rows of x: the weight-streaming kernels; more: the
+    product, then the elementwise kernel) equals the two steps apart, and the plain formula."""
+    from liteinfer_b200 import ops
+
+    x, w = _randn(M, K, seed=1, dtype=dtype), _randn(N, K, seed=2, scale=0.1, dtype=dtype)
+    got = ops.linear(x, w, None, activation=name)
+    apart = ops.linear(x, w, None)
+    product = apart.float().clone()
+    ops.activation(apart, apart, name)
+    torch.testing.assert_close(got.float(), apart.float(), rtol=2 ** -7 if dtype == torch.bfloat16 else 1e-6, atol=1e-6)
+    want = {"relu_squared": lambda v: torch.relu(v) ** 2, "silu": lambda v: v * torch.sigmoid(v),
+            "gelu_tanh": lambda v: torch.nn.functional.gelu(v, approximate="tanh")}[name](product)
+    torch.testing.assert_close(got.float(), want, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,M,N,K", [(3, 5, 40, 12), (1, 70, 33, 100), (6, 1, 24, 48), (4, 130, 64, 32)])
 def test_batched_linear_on_column_slices(dtype, B, M, N, K):
     from liteinfer_b200 import ops

@@ -97,7 +97,7 @@ def gated_linear(x, weight, out, activation, bias=None):
     return act_mul_interleaved(gate_up, out, activation)
 
 
-def linear(x, weight, out, bias=None, residual=None):
+def linear(x, weight, out, bias=None, residual=None, activation=None):
     """The product alone: a norm that is still pending runs first, and the result is never added into `residual`
     here (the caller gets it back as the delta still to be added)."""
     if hasattr(x, "materialise"):
@@ -108,6 +108,8 @@ def linear(x, weight, out, bias=None, residual=None):
     if out is None:
         out = torch.empty(y.shape, dtype=x.dtype, device=x.device)
     out.copy_(y.to(out.dtype))
+    if activation is not None:
+        _unary(out, out, activation)
     return out
 
 
@@ -409,6 +411,9 @@ def activation(x, out, name):
     v = x.float()
     out.copy_((torch.relu(v) ** 2 if name == "relu_squared" else _activate(v, name)).to(out.dtype))
     return out
+
+
+_unary = activation
 
 
 def batched_linear(x, weight, out):
